@@ -318,8 +318,8 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
-// Slow path of a flag wait: out of line on purpose -- the decode GEMMs are sensitive to their code size (a bisect in
-// round 2 attributed 1-2 % of the step to a few hundred extra SASS instructions per kernel), and this is inlined nowhere.
+// Slow path of a flag wait: out of line on purpose -- the decode GEMMs are sensitive to their code size (an A/B
+// run attributed 1-2 % of the step to three inlined copies of this path), and this is inlined nowhere.
 static __device__ __noinline__ void wait_flag_slow(const uint32_t* flag, uint32_t target) {
   volatile uint32_t* ab = g_abort_word;
   if (ab != nullptr && *ab != 0u) return;                                        // mesh aborted: drain
