@@ -22,9 +22,9 @@ BUILD = ROOT / "build" / "obj"
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CU_SOURCES = ["gemm_tc.cu", "elementwise.cu", "attention.cu", "attention_tc.cu", "sampler.cu", "hybrid.cu", "seqmix.cu"]
+CU_SOURCES = ["gemm_tc.cu", "elementwise.cu", "attention.cu", "attention_tc.cu", "sampler.cu", "hybrid.cu", "seqmix.cu", "postnorm.cu"]
 # translation units whose arithmetic must be exact fp32 (no approximate division / exp / sqrt, no flush to zero)
-EXACT_MATH = {"hybrid.cu", "seqmix.cu"}
+EXACT_MATH = {"hybrid.cu", "seqmix.cu", "postnorm.cu"}
 CPP_SOURCES = ["peer.cpp", "binding.cpp"]
 
 NVCC_FLAGS = [

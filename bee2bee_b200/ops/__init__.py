@@ -17,7 +17,9 @@ import torch
 EPI_PLAIN, EPI_RESIDUAL, EPI_GLU, EPI_QKV_ROPE, EPI_GELU = 0, 1, 2, 3, 4
 ACT_SILU, ACT_GELU, ACT_RELU_SQ, ACT_XIELU = 0, 1, 2, 3   # ``act_gelu`` of ``gemm``: GLU gate activation / EPI_GELU activation
 COLS_COPY, COLS_TANH, COLS_RELU_SQ, COLS_XIELU, COLS_SOFTCAP = 0, 1, 2, 3, 4     # ``act`` of ``act_cols``
-SCAN_GLA, SCAN_DELTA, SCAN_MLSTM = 0, 1, 2     # ``mode`` of ``lin_scan``
+SCAN_GLA, SCAN_DELTA, SCAN_MLSTM, SCAN_HGRN2 = 0, 1, 2, 3     # ``mode`` of ``lin_scan``
+POST_SIGMOID, POST_SILU, POST_NONE = 0, 1, 2     # ``act`` of ``scan_post``: the output gate
+GATE_SILU, GATE_GELU, GATE_GELU_TANH = 0, 1, 2   # ``act`` of ``gated_cols`` (GELU = the exact erf form)
 PAGE = 64           # tokens per KV page (csrc/attention.cu)
 NUM_SMS = 148
 
@@ -32,7 +34,8 @@ _KERNEL_ENTRY_POINTS = ("add", "attention", "decode_advance", "embed", "fetch_wi
                         "kv_append", "layernorm", "mark_seen", "quant_fp8_rows", "quant_mxfp8_rows", "rmsnorm", "sample",
                         "set_decode_state", "hyb_embed", "hyb_commit_prev", "hc_step", "act_cols", "attn_prep",
                         "sig_attention", "delta_scan", "delta_post", "ls_join", "rot_attn_prep", "softmax_attention",
-                        "short_conv", "mlstm_gates", "lin_scan", "scan_post")
+                        "short_conv", "mlstm_gates", "lin_scan", "scan_post", "post_norm_join", "latent_prep", "rot_heads",
+                        "moe_route", "gated_cols")
 
 
 class _CountedModule:
@@ -576,3 +579,35 @@ def lin_scan(mode, qk, off_q, off_k, v, off_v, state, out, q_start, q_len, kv_le
 def scan_post(o, gate, off_g, weight, act, aux, out, T, H, dv, eps):
     """per-head output norm x weight x gate (``act`` 0 sigmoid, 1 silu); ``aux``: mLSTM denominators"""
     native().scan_post(o, gate, off_g, weight, act, aux, out, T, H, dv, eps)
+
+
+# ------------------------------------------------------- post-norm hybrids (the norm follows the residual addition; latent attention, routed experts)
+def post_norm_join(x, *, w, h, y=None, gate=None, off_g=0, gbias=None, idw=None, alpha=1.0, groups=1, eps=1e-6, rows=None,
+                   n_rows=0):
+    """``x <- groupnorm(alpha x + s (y + idw x)) * w`` with ``s = sigmoid(gate[:, off_g:] + gbias)`` (1 without a gate),
+    the norm taken over ``groups`` consecutive parts of the width; ``h`` receives the new residual as the operand of the
+    next matrix product.  ``rows`` (with ``n_rows``): only ``h[r] = groupnorm(alpha x[rows[r]]) * w`` is written."""
+    native().post_norm_join(x, rows, n_rows if rows is not None else x.shape[0], y, gate, off_g, gbias, idw, float(alpha), w,
+                            groups, float(eps), h)
+
+
+def latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, eps, T):
+    """latent attention: normed query latent -> ``cq``; cache row ``[rotated shared key part (R) | normed latent (C)]``"""
+    native().latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, float(eps), T)
+
+
+def rot_heads(src, off, dst, H, Dh, freq, rdims, positions, T, slots=None):
+    """``dst`` [T, H * Dh] (dense) = the ``H`` heads of ``Dh`` channels at column ``off`` of ``src`` with rotary positions
+    on the first ``rdims`` channels (pairs 2i, 2i+1) of each head"""
+    native().rot_heads(src, off, dst, H, Dh, freq, rdims, positions, slots, T)
+
+
+def moe_route(proj, off, corr, n_real, count, keep, top, scale, wt, idw, T, sel_idx=None, sel_w=None):
+    """softmax router over ``corr.numel()`` outputs (the last ones beyond ``n_real`` are identity experts): dense weight
+    rows ``wt`` [T, n_real] and the summed identity weight ``idw`` [T]; optionally the choices in order"""
+    native().moe_route(proj, off, corr, n_real, count, keep, top, float(scale), wt, idw, sel_idx, sel_w, T)
+
+
+def gated_cols(x, off_a, off_b, out, n, act, T, wt=None, per=0):
+    """``out[t, c] = act(x[t, off_a + c]) * x[t, off_b + c]``, or ``* wt[t, c // per]`` with per-expert weights"""
+    native().gated_cols(x, off_a, off_b, wt, per, out, n, act, T)

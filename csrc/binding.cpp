@@ -584,7 +584,8 @@ void softmax_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                                       static_cast<int>(block_table.stride(0)), ip(q_start), ip(q_len), ip(kv_len),
                                       static_cast<int>(n_seqs), static_cast<int>(max_q), static_cast<int>(H),
                                       static_cast<int>(G), static_cast<int>(D), static_cast<int>(V),
-                                      static_cast<int>(window), static_cast<float>(scale), is_f32(out), cur_stream()),
+                                      static_cast<int>(window), static_cast<float>(scale),
+                                      static_cast<int>(v_cache.stride(1)), is_f32(out), cur_stream()),
         "softmax_attention");
 }
 
@@ -646,6 +647,74 @@ void scan_post(const Tensor& o, const Tensor& gate, int64_t off_g, const Tensor&
                               is_f32(out), cur_stream()),
         "scan_post");
 }
+
+// ---- post-norm layers, latent attention prep, router, gated columns (csrc/postnorm.cu)
+void post_norm_join(const Tensor& x, const OptT& rows, int64_t n_rows, const OptT& y, const OptT& gate, int64_t off_g,
+                    const OptT& gbias, const OptT& idw, double alpha, const Tensor& w, int64_t groups, double eps,
+                    const Tensor& h) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const bool has_gate = gate.has_value() && gate->defined();
+  TORCH_CHECK(!has_gate || (gbias.has_value() && gbias->defined()), "post_norm_join: the gate comes with its bias");
+  auto ld = [](const OptT& t) { return (t.has_value() && t->defined()) ? static_cast<int>(t->stride(0)) : 0; };
+  check(b2b::launch_post_norm_join(const_cast<float*>(fp(x)), (rows.has_value() && rows->defined()) ? ip(*rows) : nullptr,
+                                   static_cast<int>(n_rows), fp_or_null(y), ld(y), fp_or_null(gate), ld(gate),
+                                   static_cast<int>(off_g), fp_or_null(gbias), fp_or_null(idw), static_cast<float>(alpha),
+                                   fp(w), static_cast<int>(groups), static_cast<float>(eps), h.data_ptr(),
+                                   static_cast<int>(h.stride(0)), static_cast<int>(x.size(-1)), is_f32(h), cur_stream()),
+        "post_norm_join");
+}
+
+void latent_prep(const Tensor& proj, int64_t off_q, int64_t q_rank, int64_t off_kv, int64_t C, int64_t R, const Tensor& wq,
+                 const Tensor& wc, const Tensor& freq, int64_t rdims, const Tensor& positions, const Tensor& slots,
+                 const Tensor& cq, const Tensor& k_cache, double eps, int64_t T) {
+  c10::cuda::CUDAGuard guard(proj.device());
+  TORCH_CHECK(cq.scalar_type() == k_cache.scalar_type(), "latent_prep: operand and cache dtypes must match");
+  TORCH_CHECK(k_cache.size(-1) == R + C && k_cache.is_contiguous(), "latent_prep: cache rows are [rotary | latent]");
+  TORCH_CHECK(rdims == 0 || freq.numel() >= rdims / 2, "latent_prep: frequency table too short");
+  check(b2b::launch_latent_prep(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off_q),
+                                static_cast<int>(q_rank), static_cast<int>(off_kv), static_cast<int>(C),
+                                static_cast<int>(R), fp(wq), fp(wc), fp(freq), static_cast<int>(rdims), ip(positions),
+                                ip(slots), cq.data_ptr(), static_cast<int>(cq.stride(0)), k_cache.data_ptr(),
+                                static_cast<float>(eps), static_cast<int>(T), is_f32(cq), cur_stream()),
+        "latent_prep");
+}
+
+void rot_heads(const Tensor& src, int64_t off, const Tensor& dst, int64_t H, int64_t Dh, const Tensor& freq, int64_t rdims,
+               const Tensor& positions, const OptT& slots, int64_t T) {
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(rdims == 0 || freq.numel() >= rdims / 2, "rot_heads: frequency table too short");
+  TORCH_CHECK(dst.is_contiguous() && dst.size(-1) == H * Dh, "rot_heads: dense [T, H * Dh] output");
+  check(b2b::launch_rot_heads(fp(src), static_cast<int>(src.stride(0)), static_cast<int>(off), const_cast<float*>(fp(dst)),
+                              static_cast<int>(H), static_cast<int>(Dh), fp(freq), static_cast<int>(rdims), ip(positions),
+                              (slots.has_value() && slots->defined()) ? ip(*slots) : nullptr, static_cast<int>(T),
+                              cur_stream()),
+        "rot_heads");
+}
+
+void moe_route(const Tensor& proj, int64_t off, const Tensor& corr, int64_t n_real, int64_t count, int64_t keep,
+               int64_t top, double scale, const Tensor& wt, const Tensor& idw, const OptT& sel_idx, const OptT& sel_w,
+               int64_t T) {
+  c10::cuda::CUDAGuard guard(proj.device());
+  const bool has_sel = sel_idx.has_value() && sel_idx->defined();
+  check(b2b::launch_moe_route(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off), fp(corr),
+                              static_cast<int>(corr.numel()), static_cast<int>(n_real), static_cast<int>(count),
+                              static_cast<int>(keep), static_cast<int>(top), static_cast<float>(scale),
+                              const_cast<float*>(fp(wt)), static_cast<int>(wt.stride(0)), const_cast<float*>(fp(idw)),
+                              has_sel ? const_cast<int*>(ip(*sel_idx)) : nullptr,
+                              const_cast<float*>(fp_or_null(sel_w)), static_cast<int>(T), cur_stream()),
+        "moe_route");
+}
+
+void gated_cols(const Tensor& in, int64_t off_a, int64_t off_b, const OptT& wt, int64_t per, const Tensor& out, int64_t n,
+                int64_t act, int64_t T) {
+  c10::cuda::CUDAGuard guard(in.device());
+  const bool has_wt = wt.has_value() && wt->defined();
+  check(b2b::launch_gated_cols(fp(in), static_cast<int>(in.stride(0)), static_cast<int>(off_a), static_cast<int>(off_b),
+                               fp_or_null(wt), has_wt ? static_cast<int>(wt->stride(0)) : 0,
+                               static_cast<int>(per > 0 ? per : 1), out.data_ptr(), static_cast<int>(out.stride(0)),
+                               static_cast<int>(n), static_cast<int>(act), static_cast<int>(T), is_f32(out), cur_stream()),
+        "gated_cols");
+}
 }  // namespace
 
 
@@ -700,4 +769,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mlstm_gates", &mlstm_gates);
   m.def("lin_scan", &lin_scan);
   m.def("scan_post", &scan_post);
+  m.def("post_norm_join", &post_norm_join);
+  m.def("latent_prep", &latent_prep);
+  m.def("rot_heads", &rot_heads);
+  m.def("moe_route", &moe_route);
+  m.def("gated_cols", &gated_cols);
 }

@@ -102,7 +102,7 @@ int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int of
 int launch_softmax_attention(const float* q, const void* k_cache, const void* v_cache, void* out, int ld_out,
                              const int* block_table, int max_pages, const int* q_start, const int* q_len,
                              const int* kv_len, int n_seqs, int max_q, int H, int G, int D, int V, int window,
-                             float scale, int f32, cudaStream_t s);
+                             float scale, int ldv, int f32, cudaStream_t s);
 int launch_short_conv(const float* x, int ld_x, int off, const float* w, float* tail, float* y, int ld_y,
                       const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs,
                       int max_q, int C, int taps, cudaStream_t s);
@@ -110,7 +110,8 @@ int launch_mlstm_gates(const float* proj, int ld, int off_q, int off_k, int off_
                        const float* bf_, float cap, float qscale, float* nstate, float* mstate, float* aux,
                        const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
                        int dk, cudaStream_t s);
-// mode: 0 diag-gated linear attention, 1 delta rule with channel decay, 2 mLSTM matrix memory
+// mode: 0 diag-gated linear attention, 1 delta rule with channel decay, 2 mLSTM matrix memory, 3 HGRN2 (forget gate with a
+// lower bound, its complement is the write strength; hparam = the bound [H * dk], z = the gate projection, no keys)
 int launch_lin_scan(int mode, const float* qk, int ld_qk, int off_q, int off_k, const float* v, int ld_v, int off_v,
                     const float* z, int ld_z, int off_z, const float* zbias, const float* hparam, const float* beta,
                     int ld_b, int off_b, const float* aux, float qscale, float inv_tau, float* state, float* out,
@@ -119,6 +120,25 @@ int launch_lin_scan(int mode, const float* qk, int ld_qk, int off_q, int off_k, 
 int launch_scan_post(const float* o, int ld_o, const float* gate, int ld_g, int off_g, const float* weight, int wshared,
                      int act, const float* aux, void* out, int ld_out, int T, int H, int dv, float eps, int f32,
                      cudaStream_t s);
+
+// postnorm.cu: post-norm layers (grouped RMS norm behind the residual addition, scaled skip, sigmoid-gated sublayer results), latent
+// attention prep (normed query latent; cache row = [rotated shared key part | normed latent]), rotary positions on the first
+// channels of every head (-> dense query rows), softmax router (selection-only correction, group-limited top-k, identity experts),
+// act(a) * b over column blocks or per-expert weights.  ldv of launch_softmax_attention: row stride of the value view
+// (0 = a cache of its own) so that values can be a slice of the key rows.
+int launch_post_norm_join(float* x, const int* rows, int n_rows, const float* y, int ld_y, const float* gate, int ld_g,
+                          int off_g, const float* gbias, const float* idw, float alpha, const float* w, int groups,
+                          float eps, void* h, int ld_h, int W, int f32, cudaStream_t s);
+int launch_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int C, int R, const float* wq,
+                       const float* wc, const float* freq, int rdims, const int* positions, const int* slots, void* cq,
+                       int ld_cq, void* k_cache, float eps, int T, int f32, cudaStream_t s);
+int launch_rot_heads(const float* src, int ld, int off, float* dst, int H, int Dh, const float* freq, int rdims,
+                     const int* positions, const int* slots, int T, cudaStream_t s);
+int launch_moe_route(const float* proj, int ld, int off, const float* corr, int E, int n_real, int count, int keep,
+                     int top, float scale, float* wt, int ld_wt, float* idw, int* sel_idx, float* sel_w, int T,
+                     cudaStream_t s);
+int launch_gated_cols(const float* in, int ld_in, int off_a, int off_b, const float* wt, int ld_wt, int per, void* out,
+                      int ld_out, int n, int act, int T, int f32, cudaStream_t s);
 
 // bounded handoff waits: device abort word + time limit for the waits of each translation unit (0 / null = trap policy)
 int set_wait_policy_gemm(uint32_t* abort_word, unsigned long long limit_ns);

@@ -22,6 +22,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdint>
+
 #include "launch.cuh"
 
 namespace b2b {
@@ -314,7 +316,7 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const float* q, const
 // pass over 32 keys computes one score per lane, rescales the running sums, then the lanes own value channels.
 // grid (query tiles of 4, heads, sequences), 128 threads, dynamic smem 4 * D floats.
 constexpr int SMX_WARPS = 4;
-constexpr int SMX_VR = 8;          // value channels per lane: V <= 256
+constexpr int SMX_VR = 8;          // value channels per lane: V <= 256 (VR = 16 for wider values, V <= 512)
 constexpr int SMX_MMA_MIN_Q = 16;  // spans from this length on run on the tensor-core variant (bf16 mode)
 constexpr int SMX_MMA_WARPS = 4;   // warps (of 16 queries) per block of the tensor-core variant (8 measured slower:
                                    // fewer blocks, and the early warps of a tile idle at the page barriers)
@@ -324,12 +326,12 @@ constexpr int SMX_DEC_MAX_Q = 2;   // spans up to this length run the decode var
 // WPQ = 1: a block holds SMX_WARPS queries, one warp each.  WPQ > 1 (decode steps and very short spans): a block is ONE
 // (query, head); its WPQ warps take the 32-key passes in turn and their partial (maximum, sum, values) are merged through
 // shared memory, so a long context is read by WPQ warps at once.
-template <typename CT, typename OT, int WPQ>
+template <typename CT, typename OT, int WPQ, int VR = SMX_VR>
 __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
     softmax_attention_kernel(const float* __restrict__ q, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
                              OT* __restrict__ out, int ld_out, const int* __restrict__ block_table, int max_pages,
                              const int* __restrict__ q_start, const int* __restrict__ q_len,
-                             const int* __restrict__ kv_len, int H, int G, int D, int V, int window, float scale) {
+                             const int* __restrict__ kv_len, int H, int G, int D, int V, int window, float scale, int ldv) {
   pdl_begin();
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -352,9 +354,9 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
   }
   const int* bt = block_table + static_cast<size_t>(s) * max_pages;
   const bool kvec = (D * sizeof(CT)) % 16 == 0;
-  float acc[SMX_VR];
+  float acc[VR];
 #pragma unroll
-  for (int r = 0; r < SMX_VR; ++r) acc[r] = 0.f;
+  for (int r = 0; r < VR; ++r) acc[r] = 0.f;
   float mx = -INFINITY, den = 0.f;
   const int stride = WPQ > 1 ? 32 * WPQ : 32;
   for (int j0 = lo + (WPQ > 1 ? 32 * warp : 0); j0 <= pi; j0 += stride) {
@@ -371,14 +373,14 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
     den = den * corr + warp_sum_(p);
     mx = nmx;
 #pragma unroll
-    for (int r = 0; r < SMX_VR; ++r) acc[r] *= corr;
+    for (int r = 0; r < VR; ++r) acc[r] *= corr;
     const int cnt = min(32, pi - j0 + 1);
     for (int jj = 0; jj < cnt; ++jj) {
       const float w = __shfl_sync(0xffffffffu, p, jj);
       const long long sl = __shfl_sync(0xffffffffu, slot, jj);
-      const CT* vrow = v_cache + (static_cast<size_t>(sl) * G + g) * V;
+      const CT* vrow = v_cache + static_cast<size_t>(sl) * ldv + g * V;
 #pragma unroll
-      for (int r = 0; r < SMX_VR; ++r) {
+      for (int r = 0; r < VR; ++r) {
         const int d = lane + 32 * r;
         if (d < V) acc[r] += w * ldf(vrow, d);
       }
@@ -393,7 +395,7 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
       part[warp * ps + 1] = den;
     }
 #pragma unroll
-    for (int r = 0; r < SMX_VR; ++r) {
+    for (int r = 0; r < VR; ++r) {
       const int d = lane + 32 * r;
       if (d < V) part[warp * ps + 2 + d] = acc[r];
     }
@@ -403,12 +405,12 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
     for (int w = 0; w < WPQ; ++w) M = fmaxf(M, part[w * ps]);
     den = 0.f;
 #pragma unroll
-    for (int r = 0; r < SMX_VR; ++r) acc[r] = 0.f;
+    for (int r = 0; r < VR; ++r) acc[r] = 0.f;
     for (int w = 0; w < WPQ; ++w) {
       const float c = expf(part[w * ps] - M);            // a warp that saw no key: exp(-inf) = 0
       den += part[w * ps + 1] * c;
 #pragma unroll
-      for (int r = 0; r < SMX_VR; ++r) {
+      for (int r = 0; r < VR; ++r) {
         const int d = lane + 32 * r;
         if (d < V) acc[r] += part[w * ps + 2 + d] * c;
       }
@@ -416,7 +418,7 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
   }
   const float inv = 1.f / den;
 #pragma unroll
-  for (int r = 0; r < SMX_VR; ++r) {
+  for (int r = 0; r < VR; ++r) {
     const int d = lane + 32 * r;
     if (d < V) stf(out, static_cast<size_t>(t) * ld_out + hd * V + d, acc[r] * inv);
   }
@@ -448,32 +450,40 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
                                  const bf16* __restrict__ v_cache, bf16* __restrict__ out, int ld_out,
                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
                                  const int* __restrict__ q_len, const int* __restrict__ kv_len, int H, int G, int D,
-                                 int V, int window, float scale) {
+                                 int V, int window, float scale, int ldv, int hg) {
+  // hg == 1: a block = 64 consecutive queries of one head (blockIdx.y).  hg > 1 (= H / G): the hg query heads that share
+  // key/value head blockIdx.y are stacked into the rows of the tile, row r = (query r / hg, head r % hg of the group), so a
+  // page is staged once for all of them and a decode step of one sequence fills hg rows instead of one.
   pdl_begin();
   constexpr int DP = 16 * DT, VP = 16 * VT, KS = DP + 8, VS = VP + 8;
   __shared__ __align__(16) bf16 Ks[64 * KS];
   __shared__ __align__(16) bf16 Vs[64 * VS];
-  const int s = blockIdx.z, hd = blockIdx.y, n = q_len[s];
-  constexpr int QT = 16 * SMX_MMA_WARPS;          // queries per block
+  const int s = blockIdx.z, nq = q_len[s], n = nq * hg;
+  constexpr int QT = 16 * SMX_MMA_WARPS;          // rows per block
   const int ib = blockIdx.x * QT;
   if (ib >= n) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
-  const int t0 = q_start[s], pos0 = kv_len[s] - n;
-  const int g = hd / (H / G);
+  const int t0 = q_start[s], pos0 = kv_len[s] - nq;
+  const int g = hg > 1 ? static_cast<int>(blockIdx.y) : static_cast<int>(blockIdx.y) / (H / G);
   const int i_r0 = ib + warp * 16 + gid, i_r1 = i_r0 + 8;
   const bool ok0 = i_r0 < n, ok1 = i_r1 < n;
-  const int p0 = pos0 + i_r0, p1 = pos0 + i_r1;
+  // query index within the span and head of the two rows this thread holds (clamped to the block's first row when idle)
+  const int rr0 = ok0 ? i_r0 : ib, rr1 = ok1 ? i_r1 : ib;
+  const int qi0 = rr0 / hg, qi1 = rr1 / hg;
+  const int hd0 = hg > 1 ? g * hg + rr0 % hg : static_cast<int>(blockIdx.y);
+  const int hd1 = hg > 1 ? g * hg + rr1 % hg : static_cast<int>(blockIdx.y);
+  const int p0 = pos0 + qi0, p1 = pos0 + qi1;
   const int lo0 = window > 0 ? max(0, p0 - window + 1) : 0, lo1 = window > 0 ? max(0, p1 - window + 1) : 0;
-  const int pfirst = pos0 + ib, pmax = pos0 + min(n, ib + QT) - 1;
+  const int pfirst = pos0 + ib / hg, pmax = pos0 + (min(n, ib + QT) - 1) / hg;
   const int lo_min = window > 0 ? max(0, pfirst - window + 1) : 0;
   const int wi0 = ib + warp * 16;
   const bool wact = wi0 < n;
-  const int wpmin = pos0 + wi0, wpmax = pos0 + min(n - 1, wi0 + 15);
+  const int wpmin = pos0 + wi0 / hg, wpmax = pos0 + min(n - 1, wi0 + 15) / hg;
   const int wlo = window > 0 ? max(0, wpmin - window + 1) : 0;
   unsigned qa[DT][4];
   {
-    const float* q0 = q + (static_cast<size_t>(t0 + (ok0 ? i_r0 : ib)) * H + hd) * D;
-    const float* q1 = q + (static_cast<size_t>(t0 + (ok1 ? i_r1 : ib)) * H + hd) * D;
+    const float* q0 = q + (static_cast<size_t>(t0 + qi0) * H + hd0) * D;
+    const float* q1 = q + (static_cast<size_t>(t0 + qi1) * H + hd1) * D;
 #pragma unroll
     for (int kk = 0; kk < DT; ++kk) {
       const int c0 = kk * 16 + 2 * tig, c1 = c0 + 8;
@@ -495,7 +505,7 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
     __syncthreads();                           // every warp is done with the previous tile
     {
       const bf16* ksrc = k_cache + (page * 64 * G + g) * D;
-      const bf16* vsrc = v_cache + (page * 64 * G + g) * V;
+      const bf16* vsrc = v_cache + page * 64 * ldv + g * V;
       constexpr int KC = DP / 8, VC = VP / 8;
       for (int idx = threadIdx.x; idx < 64 * KC; idx += 32 * SMX_MMA_WARPS) {
         const int r = idx / KC, c8 = idx % KC;
@@ -508,7 +518,7 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         // rows past the newest key of the block may hold anything (a page that is used again): P = 0 there, but
         // 0 * NaN would still spoil the sum, so they are staged as zeros
-        if (c8 * 8 < V && kb + r <= pmax) v = *reinterpret_cast<const uint4*>(vsrc + static_cast<size_t>(r) * G * V + c8 * 8);
+        if (c8 * 8 < V && kb + r <= pmax) v = *reinterpret_cast<const uint4*>(vsrc + static_cast<size_t>(r) * ldv + c8 * 8);
         *reinterpret_cast<uint4*>(Vs + r * VS + c8 * 8) = v;
       }
     }
@@ -590,12 +600,12 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
     const int col = vt * 8 + 2 * tig;
     if (col >= V) continue;
     if (ok0) {
-      const size_t t = static_cast<size_t>(t0 + i_r0);
-      *reinterpret_cast<unsigned*>(out + t * ld_out + hd * V + col) = pack_bf16x2(oacc[vt][0] * i0, oacc[vt][1] * i0);
+      const size_t t = static_cast<size_t>(t0 + qi0);
+      *reinterpret_cast<unsigned*>(out + t * ld_out + hd0 * V + col) = pack_bf16x2(oacc[vt][0] * i0, oacc[vt][1] * i0);
     }
     if (ok1) {
-      const size_t t = static_cast<size_t>(t0 + i_r1);
-      *reinterpret_cast<unsigned*>(out + t * ld_out + hd * V + col) = pack_bf16x2(oacc[vt][2] * i1, oacc[vt][3] * i1);
+      const size_t t = static_cast<size_t>(t0 + qi1);
+      *reinterpret_cast<unsigned*>(out + t * ld_out + hd1 * V + col) = pack_bf16x2(oacc[vt][2] * i1, oacc[vt][3] * i1);
     }
   }
 }
@@ -834,11 +844,13 @@ __global__ void __launch_bounds__(32)
 //     LS_DELTA  q = unit(x_q) * qscale, k = unit(x_k)  (x after the short convolution; head h reads q/k head h / (H/G)),
 //               d = exp(-exp(A_h) softplus(z + bias)), beta = sigmoid(x_b)
 //     LS_MLSTM  q = x_q * qscale, k = take * x_k, d = keep   (keep, take from mlstm_gates)
+//     LS_HGRN2  q = silu(x_q), d = lo + (1 - lo) sigmoid(z + bias), k = 1 - d   (keyless: the write strength is the
+//               complement of the forget gate; lo [H * dk] = hparam bounds the gate from below, z is a plain projection)
 // Columns of S are independent: a block owns CB columns of one (sequence, head); LN lanes share a column group, each with
 // R key channels in registers (channel of (lane l, register m) = l + LN m; dk padded to R * LN with zeros).  Spans: while
 // the scan warps walk tile i (the only token-sequential work) the staging warps prepare tile i + 1 in the other half of a
 // double buffer; decode steps (DEC): every span is one token, all threads stage, then scan.
-enum { LS_GLA = 0, LS_DELTA = 1, LS_MLSTM = 2 };
+enum { LS_GLA = 0, LS_DELTA = 1, LS_MLSTM = 2, LS_HGRN2 = 3 };
 // staging threads of a span block (8 warps with one token each per tile measured no better than 4 with two)
 __host__ __device__ constexpr int ls_stage_threads(int) { return 128; }
 // state columns per thread: 2 for spans; 4 with 16-byte state accesses for decode steps (a stream over the states)
@@ -849,7 +861,7 @@ struct ScanArgs {
   const float* v;   int ld_v, off_v;
   const float* z;   int ld_z, off_z;              // low-rank decay projection (GLA, DELTA)
   const float* zbias;                             // [H * dk]
-  const float* hparam;                            // DELTA: A_log [H]
+  const float* hparam;                            // DELTA: A_log [H]; HGRN2: lower bound of the forget gate [H * dk]
   const float* beta; int ld_b, off_b;             // DELTA: write strength before the sigmoid
   const float* aux;                               // MLSTM: [T, H, 4]
   float qscale, inv_tau;
@@ -908,11 +920,12 @@ __global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : ls_stage_th
       }
     }
   }
-  float zb[EPL];
+  float zb[EPL], lob[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) {
     const int i = lane + 32 * e;
     zb[e] = (MODE != LS_MLSTM && stager && i < dk) ? a.zbias[hd * dk + i] : 0.f;
+    lob[e] = (MODE == LS_HGRN2 && stager && i < dk) ? a.hparam[hd * dk + i] : 0.f;
   }
   const float rate = MODE == LS_DELTA ? expf(a.hparam[hd]) : 0.f;
   float pq[TPW][EPL], pk[TPW][EPL], pz[TPW][EPL], pv[TPW], pb[TPW], pd[TPW];
@@ -929,7 +942,7 @@ __global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : ls_stage_th
         const int i = lane + 32 * e;
         const bool ok = tok && i < dk;
         pq[tw][e] = ok ? qrow[a.off_q + i] : 0.f;
-        pk[tw][e] = ok ? qrow[a.off_k + i] : 0.f;
+        pk[tw][e] = (MODE != LS_HGRN2 && ok) ? qrow[a.off_k + i] : 0.f;
         if (MODE != LS_MLSTM) pz[tw][e] = ok ? a.z[t * a.ld_z + a.off_z + hd * dk + i] : 0.f;
       }
       pv[tw] = 0.f;
@@ -971,8 +984,14 @@ __global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : ls_stage_th
           if (MODE == LS_GLA) d = expf(logsigmoid_(pz[tw][e] + zb[e]) * a.inv_tau);
           if (MODE == LS_DELTA) d = expf(-rate * softplus_(pz[tw][e] + zb[e]));
           if (MODE == LS_MLSTM) d = pd[tw];
-          qs[tt * DKP + i] = pq[tw][e] * rq;
-          ks[tt * DKP + i] = pk[tw][e] * rk;
+          if (MODE == LS_HGRN2) {
+            d = lob[e] + (1.f - lob[e]) * sigmoid_(pz[tw][e] + zb[e]);
+            qs[tt * DKP + i] = silu_(pq[tw][e]);
+            ks[tt * DKP + i] = ok ? 1.f - d : 0.f;
+          } else {
+            qs[tt * DKP + i] = pq[tw][e] * rq;
+            ks[tt * DKP + i] = pk[tw][e] * rk;
+          }
           ds[tt * DKP + i] = ok ? d : 0.f;
         }
       }
@@ -1085,7 +1104,7 @@ __global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : ls_stage_th
 }
 
 // o [T, H*dv] fp32 -> per head: (o / den) / sqrt(mean(.^2) + eps) * weight * act(gate) -> OT.  den (aux given, mLSTM):
-// max(|n.q|, exp(-mx)) + 1e-6.  weight: [dv] shared by the heads (wshared) or [H*dv].  act: 0 sigmoid, 1 silu.
+// max(|n.q|, exp(-mx)) + 1e-6.  weight: [dv] shared by the heads (wshared) or [H*dv].  act: 0 sigmoid, 1 silu, 2 no gate.
 // One warp per (token, head).
 template <typename OT>
 __global__ void scan_post_kernel(const float* __restrict__ o, int ld_o, const float* __restrict__ gate, int ld_g,
@@ -1098,7 +1117,7 @@ __global__ void scan_post_kernel(const float* __restrict__ o, int ld_o, const fl
   if (wid >= static_cast<long long>(T) * H) return;
   const int t = static_cast<int>(wid / H), hd = static_cast<int>(wid % H);
   const float* src = o + static_cast<size_t>(t) * ld_o + hd * dv;
-  const float* grow = gate + static_cast<size_t>(t) * ld_g + off_g + hd * dv;
+  const float* grow = act == 2 ? src : gate + static_cast<size_t>(t) * ld_g + off_g + hd * dv;
   float inv = 1.f;
   if (aux != nullptr) {
     const float4 g = *reinterpret_cast<const float4*>(aux + (static_cast<size_t>(t) * H + hd) * 4);
@@ -1112,7 +1131,7 @@ __global__ void scan_post_kernel(const float* __restrict__ o, int ld_o, const fl
   ss = warp_sum_(ss);
   const float r = inv / sqrtf(ss / static_cast<float>(dv) + eps);
   for (int d = lane; d < dv; d += 32) {
-    const float gv = act == 1 ? silu_(grow[d]) : sigmoid_(grow[d]);
+    const float gv = act == 2 ? 1.f : (act == 1 ? silu_(grow[d]) : sigmoid_(grow[d]));
     stf(out, static_cast<size_t>(t) * ld_out + hd * dv + d, src[d] * r * weight[wshared ? d : hd * dv + d] * gv);
   }
 }
@@ -1195,11 +1214,16 @@ int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int of
 int launch_softmax_attention(const float* q, const void* k_cache, const void* v_cache, void* out, int ld_out,
                              const int* block_table, int max_pages, const int* q_start, const int* q_len,
                              const int* kv_len, int n_seqs, int max_q, int H, int G, int D, int V, int window,
-                             float scale, int f32, cudaStream_t s) {
+                             float scale, int ldv, int f32, cudaStream_t s) {
   if (n_seqs <= 0 || max_q <= 0) return 0;
-  if (V > 32 * SMX_VR || G <= 0 || H % G != 0) return -2;
-  if (!f32 && max_q >= SMX_MMA_MIN_Q && D % 8 == 0 && V % 8 == 0 && D <= 128 && V <= 128 && ld_out % 2 == 0) {
-    dim3 mgrid((max_q + 16 * SMX_MMA_WARPS - 1) / (16 * SMX_MMA_WARPS), H, n_seqs);
+  if (V > 64 * SMX_VR || G <= 0 || H % G != 0) return -2;
+  const bool wide_v = V > 32 * SMX_VR;      // values of 257 .. 512 channels: 16 channels per lane
+  if (ldv <= 0) ldv = G * V;               // values in a cache of their own; otherwise a view into wider rows
+  // short spans and decode steps of grouped heads: the heads that share a key/value head become rows of the tile
+  const int hg = (H / G > 1 && max_q < 16 * SMX_MMA_WARPS) ? H / G : 1;
+  if (!f32 && max_q * hg >= SMX_MMA_MIN_Q && D % 8 == 0 && V % 8 == 0 && D <= 128 && V <= 128 && ld_out % 2 == 0 &&
+      ldv % 8 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0) {
+    dim3 mgrid((max_q * hg + 16 * SMX_MMA_WARPS - 1) / (16 * SMX_MMA_WARPS), hg > 1 ? G : H, n_seqs);
     const int dt = (D + 15) / 16, vt = (V + 15) / 16;
     // key / value widths in units of 16 channels, rounded up to an instantiated size
     const int dts = dt <= 2 ? 2 : (dt <= 4 ? 4 : (dt <= 6 ? 6 : 8)), vts = vt <= 2 ? 2 : (vt <= 4 ? 4 : (vt <= 5 ? 5 : (vt <= 6 ? 6 : 8)));
@@ -1207,37 +1231,36 @@ int launch_softmax_attention(const float* q, const void* k_cache, const void* v_
   if (dts == A && vts == B)                                                                                             \
     launch_kernel(softmax_attention_mma_kernel<A, B>, dim3(mgrid), dim3(32 * SMX_MMA_WARPS), 0, s, 1u, q,                              \
                   static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out), ld_out,  \
-                  block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
+                  block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale, ldv, hg);
 #define B2B_SMXROW(A) B2B_SMXMMA(A, 2) B2B_SMXMMA(A, 4) B2B_SMXMMA(A, 5) B2B_SMXMMA(A, 6) B2B_SMXMMA(A, 8)
     B2B_SMXROW(2) B2B_SMXROW(4) B2B_SMXROW(6) B2B_SMXROW(8)
 #undef B2B_SMXROW
 #undef B2B_SMXMMA
     return last_error();
   }
+#define B2B_SMX(CT, WPQ, VR_, GRID, BLOCK, SMEM)                                                                         \
+  launch_kernel(softmax_attention_kernel<CT, CT, WPQ, VR_>, dim3(GRID), dim3(BLOCK), SMEM, s, 1u, q,                     \
+                static_cast<const CT*>(k_cache), static_cast<const CT*>(v_cache), static_cast<CT*>(out), ld_out,        \
+                block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale, ldv)
+#define B2B_SMX_T(WPQ, GRID, BLOCK, SMEM)                                                                               \
+  if (f32) {                                                                                                            \
+    if (wide_v) B2B_SMX(float, WPQ, 2 * SMX_VR, GRID, BLOCK, SMEM);                                                     \
+    else B2B_SMX(float, WPQ, SMX_VR, GRID, BLOCK, SMEM);                                                                \
+  } else {                                                                                                              \
+    if (wide_v) B2B_SMX(bf16, WPQ, 2 * SMX_VR, GRID, BLOCK, SMEM);                                                      \
+    else B2B_SMX(bf16, WPQ, SMX_VR, GRID, BLOCK, SMEM);                                                                 \
+  }
   if (max_q <= SMX_DEC_MAX_Q) {
     dim3 grid(max_q, H, n_seqs);
     const size_t smem = (static_cast<size_t>((D + 3) & ~3) + SMX_DEC_WARPS * (V + 2)) * sizeof(float);
-    if (f32)
-      launch_kernel(softmax_attention_kernel<float, float, SMX_DEC_WARPS>, dim3(grid), dim3(32 * SMX_DEC_WARPS), smem, s,
-                    1u, q, static_cast<const float*>(k_cache), static_cast<const float*>(v_cache),
-                    static_cast<float*>(out), ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window,
-                    scale);
-    else
-      launch_kernel(softmax_attention_kernel<bf16, bf16, SMX_DEC_WARPS>, dim3(grid), dim3(32 * SMX_DEC_WARPS), smem, s,
-                    1u, q, static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out),
-                    ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
+    B2B_SMX_T(SMX_DEC_WARPS, grid, 32 * SMX_DEC_WARPS, smem)
     return last_error();
   }
   dim3 grid((max_q + SMX_WARPS - 1) / SMX_WARPS, H, n_seqs);
   const size_t smem = static_cast<size_t>(SMX_WARPS) * D * sizeof(float);
-  if (f32)
-    launch_kernel(softmax_attention_kernel<float, float, 1>, dim3(grid), dim3(32 * SMX_WARPS), smem, s, 1u, q,
-                  static_cast<const float*>(k_cache), static_cast<const float*>(v_cache), static_cast<float*>(out), ld_out,
-                  block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
-  else
-    launch_kernel(softmax_attention_kernel<bf16, bf16, 1>, dim3(grid), dim3(32 * SMX_WARPS), smem, s, 1u, q,
-                  static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out), ld_out,
-                  block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
+  B2B_SMX_T(1, grid, 32 * SMX_WARPS, smem)
+#undef B2B_SMX_T
+#undef B2B_SMX
   return last_error();
 }
 
@@ -1319,6 +1342,7 @@ int launch_lin_scan(int mode, const float* qk, int ld_qk, int off_q, int off_k, 
   if (mode == LS_GLA) return launch_scan_mode<LS_GLA>(a, n_seqs, max_q, s);
   if (mode == LS_DELTA) return launch_scan_mode<LS_DELTA>(a, n_seqs, max_q, s);
   if (mode == LS_MLSTM) return launch_scan_mode<LS_MLSTM>(a, n_seqs, max_q, s);
+  if (mode == LS_HGRN2) return launch_scan_mode<LS_HGRN2>(a, n_seqs, max_q, s);
   return -2;
 }
 
