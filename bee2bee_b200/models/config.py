@@ -59,7 +59,16 @@ class LayerSpec:
     ``mixer`` = "mlstm": matrix memory with exponential input gate, running maximum and normaliser (``gate_cap``).
     ``mixer`` = "gla": linear attention with a decay per key channel, ``sigmoid(z) ** (1 / tau)``, z low-rank.
     ``mixer`` = "channel_delta": delta rule with a decay per key channel, short convolutions (``conv`` taps) on q/k/v.
-    ``mixer`` = "parallel": the mixers in ``sub`` read the same input; their width-normed outputs are averaged."""
+    ``mixer`` = "parallel": the mixers in ``sub`` read the same input; their width-normed outputs are averaged.
+    ``mixer`` = "latent_attention": softmax attention whose keys and values are up-projections of one cached latent of
+    ``kv_rank`` channels per token plus ``rot_dim`` rotated key channels shared by all heads; queries are produced from a
+    latent of ``q_rank`` channels and carry ``dim`` plain + ``rot_dim`` rotated channels per head; ``window`` as above.
+    ``mixer`` = "hgrn2": linear attention without keys: the write strength of a channel is the complement of its forget
+    gate (which is bounded below by a learned vector), ``S <- diag(f) S + (1 - f) v^T``, read with ``silu`` queries.
+    ``ff_kind`` = "moe": ``experts`` small feed-forwards (``expert_ff`` wide, no gate) of which a token uses ``top``,
+    chosen by a softmax router; consecutive experts are bundled into ``route_groups`` equal groups and only the
+    ``route_keep`` best-scoring groups may supply experts; the last
+    ``identity`` outputs of the router bypass the experts (they hand the input through); weights are renormalised and multiplied by ``route_scale``."""
     mixer: str = "attention"
     heads: int = 1
     kv_heads: int = 1
@@ -76,6 +85,16 @@ class LayerSpec:
     conv: int = 0                    # channel_delta: taps of the short convolution
     rank: int = 0                    # width of the low-rank gate projections (random init only; checkpoints: tensor shape)
     sub: Tuple["LayerSpec", ...] = ()
+    q_rank: int = 0                  # latent attention: width of the query latent
+    kv_rank: int = 0                 # latent attention: width of the cached key/value latent
+    rot_dim: int = 0                 # latent attention: rotated channels per query head = width of the shared rotated key
+    experts: int = 0                 # moe: real experts
+    top: int = 0                     # moe: experts (identity ones included) a token uses
+    expert_ff: int = 0               # moe: hidden width of one expert
+    route_groups: int = 1
+    route_keep: int = 1
+    identity: int = 0                # moe: router outputs that pass the feed-forward input through unchanged
+    route_scale: float = 1.0
 
     @property
     def leaves(self) -> Tuple["LayerSpec", ...]:
@@ -85,7 +104,7 @@ class LayerSpec:
 @dataclass
 class ModelConfig:
     name: str = "tiny-llama"
-    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik | repudra
+    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik | repudra | lonulix
     vocab_size: int = 512
     hidden_size: int = 256
     n_layers: int = 2
@@ -118,7 +137,11 @@ class ModelConfig:
     pair_buckets: int = 0            # rows of the hashed (previous token, token) table, 0 = none (+1 row for "no previous")
     pair_mul_prev: int = 0
     pair_mul_cur: int = 0
-    block_layout: str = "sequential"  # sequential: norm -> mixer -> join, norm -> ff -> join; parallel: one norm feeds both
+    block_layout: str = "sequential"  # sequential: norm -> mixer -> join, norm -> ff -> join; parallel: one norm feeds both;
+    #                                   post_norm: x <- norm(skip_scale * x + sublayer(x)), no norm in front of a sublayer
+    norm_groups: int = 1             # post_norm: the RMS norm is taken over this many consecutive parts of the width
+    skip_scale: float = 1.0          # post_norm: the residual is multiplied by this before the sublayer result is added
+    gated_residual: bool = False     # post_norm: sublayer results are multiplied by sigmoid(W x + b) before the sum
     scalar_norm: bool = False        # block / model norms have ONE gain (a single number) instead of one per coordinate
     layer_scale: bool = False        # sublayer outputs are multiplied coordinate-wise by learned vectors before the join
 
@@ -130,7 +153,8 @@ class ModelConfig:
     @property
     def recurrent(self) -> bool:
         """True when some layer keeps per-sequence state besides the paged KV cache (no prefix sharing, no piece split)."""
-        return any(leaf.mixer not in ("attention", "softmax_attention") for sp in self.layer_specs for leaf in sp.leaves) \
+        return any(leaf.mixer not in ("attention", "softmax_attention", "latent_attention")
+                   for sp in self.layer_specs for leaf in sp.leaves) \
             or self.pair_buckets > 0
 
     @property
@@ -301,7 +325,88 @@ class ModelConfig:
                 "width": self.hidden_size}
 
     @staticmethod
+    def from_lonulix_dict(d: Dict, name: str = "") -> "ModelConfig":
+        """``config.json`` of a Lonulix checkpoint: ``layers`` lists {type, mixer sizes, mlp | null} per layer; types
+        ``latent_attention`` and ``hgrn2``; ``mlp.kind`` ``dense`` (gated, silu) or ``moe`` (routed gelu experts)."""
+        who = name or "lonulix"
+        specs = []
+        for lay in d["layers"]:
+            m, mlp, kind = lay.get("mixer") or {}, lay.get("mlp"), lay["type"]
+            heads, dim = int(m["heads"]), int(m["dim"])
+            vdim = int(m.get("vdim", dim))
+            if kind == "latent_attention":
+                rot_dim = int(m.get("rot_dim", 0))
+                r = m.get("rot") or {}
+                rot = RotarySpec(dims=int(r.get("dims", rot_dim)), base=float(r.get("base", 10000.0))) if rot_dim else None
+                if rot is not None and (rot.dims % 2 or rot.dims > rot_dim):
+                    raise ValueError(f"{who}: rotary dims {rot.dims} do not fit {rot_dim} rotated channels")
+                sp = LayerSpec(mixer=kind, heads=heads, kv_heads=1, dim=dim, vdim=vdim,
+                               scale=float(m.get("scale", (dim + rot_dim) ** -0.5)),
+                               window=int((m.get("mask") or {}).get("size", 0) or 0), rot=rot,
+                               q_rank=int(m["q_rank"]), kv_rank=int(m["kv_rank"]), rot_dim=rot_dim)
+            elif kind == "hgrn2":
+                sp = LayerSpec(mixer=kind, heads=heads, kv_heads=heads, dim=dim, vdim=vdim)
+            else:
+                raise ValueError(f"{who}: unknown layer type {kind!r}")
+            if mlp:
+                fk = mlp.get("kind", "dense")
+                if fk == "dense":
+                    sp.ff = int(mlp["ff"])
+                elif fk == "moe":
+                    r, g = mlp["router"], (mlp["router"].get("groups") or {})
+                    sp.ff_kind, sp.expert_ff = "moe", int(mlp["expert"]["ff"])
+                    sp.experts, sp.top, sp.identity = int(r["experts"]), int(r["top"]), int(r.get("identity", 0))
+                    sp.route_groups, sp.route_keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
+                    sp.route_scale = float(r.get("scale", 1.0))
+                    sp.ff = sp.experts * sp.expert_ff
+                    if (sp.experts + sp.identity) % sp.route_groups:
+                        raise ValueError(f"{who}: {sp.experts + sp.identity} router outputs do not form {sp.route_groups} equal groups")
+                else:
+                    raise ValueError(f"{who}: feed-forward kind {fk!r} is not implemented")
+            specs.append(sp)
+        width = int(d["width"])
+        norm = d.get("norm") or {}
+        if width % int(norm.get("groups", 1)):
+            raise ValueError(f"{who}: width {width} does not split into {norm.get('groups')} norm groups")
+        att = [sp for sp in specs if sp.mixer == "latent_attention"] or specs
+        return ModelConfig(
+            name=name or "lonulix", family="lonulix", vocab_size=int(d["vocab"]), hidden_size=width, n_layers=len(specs),
+            n_heads=max(sp.heads for sp in att), n_kv_heads=1, head_dim=max(sp.dim + sp.rot_dim for sp in att),
+            ffn_size=max([sp.ff for sp in specs] + [0]), max_position=1 << 30, norm="rms",
+            norm_eps=float(norm.get("eps", 1e-6)), act="silu", glu=True, rope_theta=0.0,
+            embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), layer_specs=tuple(specs), streams=0,
+            block_layout="post_norm", norm_groups=int(norm.get("groups", 1)),
+            skip_scale=float(d.get("postln_alpha", 1.0)), gated_residual=True)
+
+    def to_lonulix_dict(self) -> Dict:
+        layers = []
+        for sp in self.layer_specs:
+            if sp.mixer == "latent_attention":
+                m = {"dim": sp.dim, "heads": sp.heads, "kv_rank": sp.kv_rank, "q_rank": sp.q_rank, "rot_dim": sp.rot_dim,
+                     "scale": sp.scale, "vdim": sp.vdim}
+                if sp.rot is not None:
+                    m["rot"] = {"base": sp.rot.base, "dims": sp.rot.dims}
+                if sp.window:
+                    m["mask"] = {"size": sp.window}
+            else:
+                m = {"dim": sp.dim, "heads": sp.heads, "vdim": sp.vdim}
+            if not sp.ff:
+                mlp = None
+            elif sp.ff_kind == "moe":
+                mlp = {"expert": {"ff": sp.expert_ff}, "kind": "moe",
+                       "router": {"experts": sp.experts, "groups": {"count": sp.route_groups, "keep": sp.route_keep},
+                                  "identity": sp.identity, "scale": sp.route_scale, "top": sp.top}}
+            else:
+                mlp = {"ff": sp.ff, "kind": "dense"}
+            layers.append({"type": sp.mixer, "mixer": m, "mlp": mlp})
+        return {"architecture": "Lonulix", "embedding": {"scale": self.embed_scale}, "layers": layers,
+                "norm": {"eps": self.norm_eps, "groups": self.norm_groups}, "postln_alpha": self.skip_scale,
+                "vocab": self.vocab_size, "width": self.hidden_size}
+
+    @staticmethod
     def from_hf_dict(d: Dict, name: str = "") -> "ModelConfig":
+        if str(d.get("architecture", "")).lower() == "lonulix":
+            return ModelConfig.from_lonulix_dict(d, name)
         if str(d.get("architecture", "")).lower() == "kepovik":
             return ModelConfig.from_kepovik_dict(d, name)
         if str(d.get("architecture", "")).lower() == "repudra":
@@ -351,6 +456,8 @@ class ModelConfig:
             return self.to_kepovik_dict()
         if self.family == "repudra":
             return self.to_repudra_dict()
+        if self.family == "lonulix":
+            return self.to_lonulix_dict()
         if self.family == "gpt2":
             return {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "vocab_size": self.vocab_size,
                     "n_embd": self.hidden_size, "n_layer": self.n_layers, "n_head": self.n_heads,
@@ -478,6 +585,41 @@ def _repudra(name, width, vocab, layers, softcap=20.0):
 PRESETS["tiny-repudra"] = _repudra("tiny-repudra", 128, 512, [
     ("parallel", (4, 2, 32, 48, 16), (2, 32, 32), 256), ("gla", 2, 32, 64, 256), ("channel_delta", 4, 2, 32, 32, 0),
     ("parallel", (4, 2, 32, 48, 16), (2, 32, 32), 0)])
+
+
+def _lonulix(name, width, vocab, layers, groups=2, alpha=2.0, embed_scale=2.0):
+    """layers: ("latent_attention", H, dim, rot_dim, vdim, q_rank, kv_rank, window, mlp) | ("hgrn2", H, dim, vdim, mlp);
+    mlp: 0 (none) | ff (dense) | (experts, expert_ff, top, groups, keep, identity, scale)"""
+    specs = []
+    for lay in layers:
+        if lay[0] == "latent_attention":
+            _, h, d, r, v, qr, kr, win, mlp = lay
+            sp = LayerSpec(mixer="latent_attention", heads=h, kv_heads=1, dim=d, vdim=v, scale=(d + r) ** -0.5, window=win,
+                           rot=RotarySpec(dims=r, base=10000.0) if r else None, q_rank=qr, kv_rank=kr, rot_dim=r)
+        else:
+            _, h, d, v, mlp = lay
+            sp = LayerSpec(mixer="hgrn2", heads=h, kv_heads=h, dim=d, vdim=v)
+        if isinstance(mlp, tuple):
+            e, eff, top, gc, gk, ident, sc = mlp
+            sp.ff_kind, sp.experts, sp.expert_ff, sp.top, sp.route_groups, sp.route_keep = "moe", e, eff, top, gc, gk
+            sp.identity, sp.route_scale, sp.ff = ident, sc, e * eff
+        else:
+            sp.ff = int(mlp)
+        specs.append(sp)
+    att = [sp for sp in specs if sp.mixer == "latent_attention"] or specs
+    return ModelConfig(name=name, family="lonulix", vocab_size=vocab, hidden_size=width, n_layers=len(specs),
+                       n_heads=max(sp.heads for sp in att), n_kv_heads=1, head_dim=max(sp.dim + sp.rot_dim for sp in att),
+                       ffn_size=max(sp.ff for sp in specs), max_position=1 << 30, norm="rms", norm_eps=1e-5, act="silu",
+                       glu=True, rope_theta=0.0, embed_scale=embed_scale, layer_specs=tuple(specs),
+                       block_layout="post_norm", norm_groups=groups, skip_scale=alpha, gated_residual=True,
+                       eos_token_id=-1, bos_token_id=-1)
+
+
+# post-norm hybrid test preset: latent attention (window 48) with routed experts, HGRN2 with a dense gated feed-forward,
+# HGRN2 without a feed-forward, latent attention over all earlier keys with a dense feed-forward
+PRESETS["tiny-lonulix"] = _lonulix("tiny-lonulix", 128, 512, [
+    ("latent_attention", 4, 16, 8, 24, 48, 40, 48, (6, 64, 2, 4, 2, 2, 1.5)), ("hgrn2", 2, 32, 48, 192),
+    ("hgrn2", 4, 16, 16, 0), ("latent_attention", 2, 32, 16, 32, 64, 32, 0, 256)])
 PRESETS["tiny-gpt2"].vocab_size = 384
 PRESETS["tiny-gpt2"].eos_token_id = 1
 PRESETS["tiny-gpt2"].bos_token_id = 0

@@ -11,6 +11,13 @@ beside an mLSTM matrix memory, their width-normed outputs averaged; diag-gated l
 decay per key channel behind short convolutions.  Each mixer kind is a method here and a kernel family in
 ``csrc/seqmix.cu`` with its constants as arguments, so other layer mixes can be described by a config alone.
 
+Family ``lonulix``: post-norm layers -- ``x <- groupnorm(alpha x + gate * sublayer(x))``, the sublayers read the residual
+itself and their results pass a sigmoid gate computed from it.  Mixers: latent attention (keys and values are
+up-projections of ONE cached latent per token plus a rotary key slice common to all heads; served in the absorbed form, so
+the paged cache holds ``[rotated part | latent]`` rows only) and HGRN2 (keyless linear attention: a forget gate with a learned lower
+bound, and its complement as the write strength).  Feed-forward: gated silu, or routed gelu experts (softmax router, selection-only correction,
+group-limited top-k, identity experts).
+
 Same interface as ``native.NativePiece`` (the runner drives both through ``forward(BatchMeta)``): a flat batch of spans
 (prompt portions of any length beside single decoded tokens), physical KV slots and block tables from the page allocator,
 logits for the rows named by ``last_idx``.  What is new here and lives next to the shared machinery:
@@ -70,6 +77,7 @@ class _Layer:
     f: Dict[str, torch.Tensor] = field(default_factory=dict)     # small fp32 parameters
     w_up: Optional[torch.Tensor] = None
     w_down: Optional[torch.Tensor] = None
+    w_glu: Optional[torch.Tensor] = None   # post-norm dense feed-forward, bf16: [gate | up] interleaved for the gated GEMM epilogue
     mix: tuple = ()                     # parallel blocks: the mixers that read the layer's input side by side
     act_params: tuple = (0.0, 0.0)      # xIELU: softplus(p), 1/2 + softplus(q)
 
@@ -114,6 +122,7 @@ class HybridPiece:
             return tensors[name].to(device=dev, dtype=f32).contiguous()
 
         self.parallel_blocks = cfg.block_layout == "parallel"
+        self.post_norm = cfg.block_layout == "post_norm"
         # parallel blocks: the feed-forward reads the same input as the mixers, so its two GEMMs run on a second stream
         # beside the recurrences (which are sequential in the tokens and leave most SMs idle), and the second of two
         # mixers side by side on a third; B2B_HYBRID_OVERLAP=0: one stream
@@ -128,6 +137,9 @@ class HybridPiece:
             L = _Layer(spec=sp)
             if self.parallel_blocks:
                 self.L[l] = self._build_parallel_block(L, l, tensors, mat, vec)
+                continue
+            if self.post_norm:
+                self.L[l] = self._build_post_norm_layer(L, l, tensors, mat, vec)
                 continue
             if sp.mixer == "attention":
                 L.w_cat = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g")
@@ -165,7 +177,7 @@ class HybridPiece:
         self.conv_tail: Dict[str, torch.Tensor] = {}   # short convolutions: the last taps - 1 inputs [slots, taps - 1, channels]
         for l in self.layers:
             sp = cfg.layer_specs[l]
-            if self.parallel_blocks:
+            if self.parallel_blocks or self.post_norm:
                 for mx in self.L[l].mix:
                     self._alloc_mixer_state(mx, num_pages)
                 continue
@@ -193,7 +205,7 @@ class HybridPiece:
 
     def _matrices(self):
         for L in self.L.values():
-            for t in (L.w_cat, L.w_o, L.w2, L.w_up, L.w_down):
+            for t in (L.w_cat, L.w_o, L.w2, L.w_up, L.w_down, L.w_glu):
                 if t is not None:
                     yield t
             for mx in L.mix:
@@ -215,6 +227,13 @@ class HybridPiece:
         return sum(s[0].numel() * 4 for d in (self.state, self.nstate, self.mstate, self.conv_tail) for s in d.values())
 
     def n_launches(self) -> int:
+        if self.post_norm:
+            n = 3                                        # embedding, its operand copy, final norm (head GEMM: the runner)
+            for L in self.L.values():
+                n += 3 + (5 if L.spec.mixer == "latent_attention" else 3)      # fused projection, output projection, join
+                if L.spec.ff:
+                    n += 4 + (1 if L.spec.ff_kind == "moe" else 0)
+            return n
         if self.parallel_blocks:
             per = {"softmax_attention": 3, "mlstm": 4, "gla": 5, "channel_delta": 7}
             n = 2 + (1 if self.caps_logits else 0)       # embedding, final join + norm (+ soft cap; head GEMM: the runner)
@@ -238,6 +257,8 @@ class HybridPiece:
         assert seq_slot is not None, "hybrid models need BatchMeta.seq_slot (state slot of every sequence)"
         if self.parallel_blocks:
             return self._forward_parallel_blocks(m)
+        if self.post_norm:
+            return self._forward_post_norm(m)
         ops.hyb_embed(m.ids, m.positions, m.q_start, m.q_len, seq_slot, self.prev_tok, self.embed, self.pair,
                       c.pair_buckets, c.pair_mul_prev, c.pair_mul_cur, st, S, mq)
         h = self.h[:T]
@@ -332,6 +353,10 @@ class HybridPiece:
 
     def _alloc_mixer_state(self, mx: _Mix, num_pages: int) -> None:
         sp, dev, f32 = mx.spec, self.device, torch.float32
+        if sp.mixer == "latent_attention":      # one row per token: [rotated key part | latent]; the values are its latent slice
+            self.k_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, 1, sp.rot_dim + sp.kv_rank), device=dev, dtype=self.dtype)
+            self.v_cache[mx.key] = self.k_cache[mx.key][..., sp.rot_dim:]
+            return
         if sp.mixer == "softmax_attention":
             self.k_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.dim), device=dev, dtype=self.dtype)
             self.v_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.vdim), device=dev, dtype=self.dtype)
@@ -401,6 +426,151 @@ class HybridPiece:
         if self.caps_logits:
             ops.act_cols(logits, 0, logits, logits.shape[1], ops.COLS_SOFTCAP, R, p0=c.final_softcap)
         return logits
+
+    # ================================================================== post-norm layers (the norm follows the residual addition)
+    def _build_post_norm_layer(self, L: _Layer, l: int, tensors: Tensors, mat, vec) -> _Layer:
+        """Layer ``l`` of a post-norm model.  No norm sits in front of a sublayer (its input is the residual), so the residual gate of a sublayer
+        is stacked under its input projections: ONE matrix per sublayer.  Latent attention is served in the absorbed form:
+        per head the key up-projection is folded into the query up-projection (``q_h . (U_k c) = (U_k^T q_h) . c``) and
+        the value up-projection into the output projection, so attention runs over the cached rows directly."""
+        sp, p, dev = L.spec, f"l{l}.", self.device
+        q = p + "mix."
+        f64 = torch.float64
+
+        def t64(n):
+            return tensors[n].to(device=dev, dtype=f64)
+
+        def stack(ws):
+            return ops.pad_weight(torch.cat(ws, 0).to(torch.float32), 128, 64).to(self.dtype).contiguous()
+
+        mx = _Mix(spec=sp, key=f"{l}.0", idx=0)
+        W = self.cfg.hidden_size
+        if sp.mixer == "latent_attention":
+            H, D, R, V, C, Q = sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank, sp.q_rank
+            rows = [t64(q + "dq"), t64(q + "dkv")]
+            mx.off.update({"dq": 0, "dkv": Q})
+            uq, uk = t64(q + "uq").view(H, D + R, Q), t64(q + "uk").view(H, D, C)
+            uv, wo = t64(q + "uv").view(H, V, C), t64(q + "o").view(W, H, V)
+            qa = torch.cat([uq[:, D:], torch.einsum("hdc,hdq->hcq", uk, uq[:, :D])], 1)          # [H, R + C, Q]
+            mx.w2 = stack([qa.reshape(H * (R + C), Q)])
+            mx.w_o = stack([torch.einsum("whv,hvc->whc", wo, uv).reshape(W, H * C)])
+            mx.rank = Q
+            mx.f["dq.norm"], mx.f["dkv.norm"] = vec(q + "dq.norm"), vec(q + "dkv.norm")
+            freq = sp.rot.frequencies() if sp.rot is not None and sp.rot.dims > 0 else [0.0]
+            mx.f["freq"] = torch.tensor(freq, dtype=f64).to(device=dev, dtype=torch.float32)
+        elif sp.mixer == "hgrn2":
+            kd = sp.heads * sp.dim
+            rows = [t64(q + "q"), t64(q + "f"), t64(q + "v")]
+            mx.off.update({"q": 0, "f": kd, "v": 2 * kd})
+            mx.w_o = mat(q + "o")
+            for n in ("f.b", "lower", "norm"):
+                mx.f[n] = vec(q + n)
+        else:
+            raise ValueError(f"{self.cfg.name}: layer {l} has mixer {sp.mixer!r}, which post-norm layers do not have")
+        mx.off["rg"] = sum(r.shape[0] for r in rows)
+        L.w_cat = stack(rows + [t64(p + "rg1")])
+        L.f["rg1.b"], L.f["norm1"] = vec(p + "rg1.b"), vec(p + "norm1")
+        L.mix = (mx,)
+        if sp.ff:
+            L.f["rg2.b"], L.f["norm2"] = vec(p + "rg2.b"), vec(p + "norm2")
+            if sp.ff_kind == "moe":         # [router | residual gate | up-projections of all experts]; down-projections side by side
+                ups = [t64(f"{p}mlp.e{e}.up") for e in range(sp.experts)]
+                router = t64(p + "mlp.router")
+                pad = router.new_zeros(((-router.shape[0]) % 4, W))      # the blocks behind it start at multiples of four
+                L.w_up = stack([router, pad, t64(p + "rg2")] + ups)
+                L.w_down = stack([torch.cat([t64(f"{p}mlp.e{e}.down") for e in range(sp.experts)], 1)])
+                L.f["correction"] = vec(p + "mlp.correction")
+            elif self.dtype == torch.bfloat16 and sp.ff % 64 == 0 and os.environ.get("B2B_POSTNORM_GLU", "0") == "1":
+                # optional: the gated-silu epilogue of the tcgen05 GEMM writes the bf16 hidden rows itself (each 128-row tile
+                # holds 64 gate and 64 up rows); the residual gate then needs a GEMM of its own with fp32 output.  Measured
+                # on B200: prefill + 0.5 %, decode steps 2-4 % slower at widths 1024 / 2048 (two more GEMM launches per step
+                # against two small elementwise launches less), so the stacked GEMM below is the default
+                gu = ops.glu_interleave_rows(t64(p + "mlp.gate").float(), t64(p + "mlp.up").float())
+                L.w_glu = ops.pad_weight(gu, 128, 64).to(self.dtype).contiguous()
+                L.w_up = stack([t64(p + "rg2")])
+                L.w_down = mat(p + "mlp.down")
+            else:                           # [gate | up | residual gate], activation by a kernel of its own
+                L.w_up = stack([t64(p + "mlp.gate"), t64(p + "mlp.up"), t64(p + "rg2")])
+                L.w_down = mat(p + "mlp.down")
+        return L
+
+    def _forward_post_norm(self, m) -> torch.Tensor:
+        """x = scale * embed;  per sublayer: x <- groupnorm(alpha x + sigmoid(R x + b) * sublayer(x)) * w;  logits =
+        head(groupnorm(x) * w).  The residual lives in fp32; ``h`` is its copy in the operand type of the matrix products."""
+        c = self.cfg
+        T, S, mq = m.n_tokens, m.n_seqs, m.max_q
+        W, f32 = c.hidden_size, torch.float32
+        norm = dict(alpha=c.skip_scale, groups=c.norm_groups, eps=c.norm_eps)
+        x = self.streams[:T].view(T, W)
+        ops.hyb_embed(m.ids, m.positions, m.q_start, m.q_len, m.seq_slot, self.prev_tok, self.embed, None, 0, 0, 0,
+                      self.streams[:T], S, mq, scale=c.embed_scale)
+        h = self.h[:T]
+        ops.act_cols(x, 0, h, W, ops.COLS_COPY, T)
+        for l in self.layers:
+            L = self.L[l]
+            mx = L.mix[0]
+            proj = ops.linear(L.w_cat, h, self._buf("proj", f32, L.w_cat.shape[0])[:T])
+            y = getattr(self, "_mix_" + mx.spec.mixer)(mx, proj, m, self._buf("y0", f32, mx.w_o.shape[0])[:T])
+            gate = dict(gate=proj, off_g=mx.off["rg"], gbias=L.f["rg1.b"]) if c.gated_residual else {}
+            ops.post_norm_join(x, w=L.f["norm1"], h=h, y=y, **gate, **norm)
+            if L.spec.ff:
+                sp = L.spec
+                p2 = ops.linear(L.w_up, h, self._buf("proj2", f32, L.w_up.shape[0])[:T])
+                hid = self._buf("ff", self.dtype, L.w_down.shape[1])[:T]
+                idw = None
+                if sp.ff_kind == "moe":
+                    n_out = ops.pad_to(sp.experts + sp.identity, 4)      # router rows (zero-padded), then gate, then experts
+                    wt = self._buf("route", f32, max(1, sp.experts))[:T]
+                    idw = self._buf("keep", f32, 1)[:T]
+                    ops.moe_route(p2, 0, L.f["correction"], sp.experts, sp.route_groups, sp.route_keep, sp.top,
+                                  sp.route_scale, wt, idw, T)
+                    ops.gated_cols(p2, n_out + W, 0, hid, sp.experts * sp.expert_ff, ops.GATE_GELU, T, wt=wt, per=sp.expert_ff)
+                    off_g = n_out
+                    if not sp.identity:
+                        idw = None
+                elif L.w_glu is not None:
+                    ops.gemm(L.w_glu, h, out=hid, epi=ops.EPI_GLU, act_gelu=ops.ACT_SILU)
+                    off_g = 0
+                else:
+                    ops.gated_cols(p2, 0, sp.ff, hid, sp.ff, ops.GATE_SILU, T)
+                    off_g = 2 * sp.ff
+                y = ops.linear(L.w_down, hid, self._buf("yff", f32, L.w_down.shape[0])[:T])
+                gate = dict(gate=p2, off_g=off_g, gbias=L.f["rg2.b"]) if c.gated_residual else {}
+                ops.post_norm_join(x, w=L.f["norm2"], h=h, y=y, idw=idw, **gate, **norm)
+            if self.debug_layers is not None:
+                self.debug_layers.append(x[:T].clone())
+        R = m.n_out or S
+        rows = m.last_idx if m.last_idx is not None else m.q_start
+        xl = self.last_x[:R]
+        ops.post_norm_join(x, w=self.final_norm, h=xl, rows=rows, n_rows=R, alpha=1.0, groups=c.norm_groups, eps=c.norm_eps)
+        return ops.linear(self.w_head, xl, self.logits[:R])
+
+    def _mix_latent_attention(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        H, R, C, Q = sp.heads, sp.rot_dim, sp.kv_rank, sp.q_rank
+        kc, vc = self.k_cache[mx.key], self.v_cache[mx.key]
+        rdims = sp.rot.dims if sp.rot is not None else 0
+        cq = self._buf(f"cq{Q}", self.dtype, mx.w2.shape[1])[:T]
+        ops.latent_prep(proj, mx.off["dq"], Q, mx.off["dkv"], C, R, mx.f["dq.norm"], mx.f["dkv.norm"], mx.f["freq"], rdims,
+                        m.positions, m.slots, cq, kc, self.cfg.norm_eps, T)
+        qa = ops.linear(mx.w2, cq, self._buf("qa", torch.float32, mx.w2.shape[0])[:T])
+        q = self._buf("q0", torch.float32, H * (R + C))[:T]
+        ops.rot_heads(qa, 0, q, H, R + C, mx.f["freq"], rdims, m.positions, T, slots=m.slots)
+        ao = self._buf(f"mix0.{H * C}", self.dtype, mx.w_o.shape[1])[:T]
+        ops.softmax_attention(q, kc, vc, ao, m.block_table, m.q_start, m.q_len, m.kv_len, m.n_seqs, m.max_q, H, 1, R + C, C,
+                              sp.window, sp.scale)
+        return ops.linear(mx.w_o, ao, y)
+
+    def _mix_hgrn2(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        H, dk, dv = sp.heads, sp.dim, sp.vdim
+        o = self._buf("o0", torch.float32, H * dv)[:T]
+        ops.lin_scan(ops.SCAN_HGRN2, proj, mx.off["q"], mx.off["q"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
+                     m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, z=proj, off_z=mx.off["f"],
+                     zbias=mx.f["f.b"], hparam=mx.f["lower"])
+        do = self._buf(f"mix0.{H * dv}", self.dtype, mx.w_o.shape[1])[:T]
+        ops.scan_post(o, o, 0, mx.f["norm"], ops.POST_NONE, None, do, T, H, dv, self.cfg.norm_eps)
+        return ops.linear(mx.w_o, do, y)
 
     def _ff(self, L: _Layer, h: torch.Tensor, T: int) -> torch.Tensor:
         """down(xIELU(up(h))): the activation is the epilogue of the up-projection"""

@@ -146,9 +146,48 @@ def repudra_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, l
     return specs
 
 
+def lonulix_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
+    """(checkpoint name, shape, kind) of a Lonulix model; matrices are kept as [out, in].  Kinds as above, plus
+    "frac" (a lower bound in (0, 1)) and "corr" (selection-only router correction, small against 1 / outputs)."""
+    W = cfg.hidden_size
+    specs = []
+    if first:
+        specs.append(("embed", (cfg.vocab_size, W), "w"))
+    for l in layers:
+        sp, p = cfg.layer_specs[l], f"l{l}."
+        m = p + "mix."
+        specs.append((p + "norm1", (W,), "one"))
+        if sp.mixer == "latent_attention":
+            H, D, R, V, C, Q = sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank, sp.q_rank
+            specs += [(m + "dq", (Q, W), "w"), (m + "dq.norm", (Q,), "one"), (m + "uq", (H * (D + R), Q), "w"),
+                      (m + "dkv", (C + R, W), "w"), (m + "dkv.norm", (C,), "one"), (m + "uk", (H * D, C), "w"),
+                      (m + "uv", (H * V, C), "w"), (m + "o", (W, H * V), "w")]
+        elif sp.mixer == "hgrn2":
+            kd, vd = sp.heads * sp.dim, sp.heads * sp.vdim
+            specs += [(m + "q", (kd, W), "w"), (m + "f", (kd, W), "w"), (m + "f.b", (kd,), "bias"),
+                      (m + "lower", (kd,), "frac"), (m + "v", (vd, W), "w"), (m + "norm", (sp.vdim,), "one"),
+                      (m + "o", (W, vd), "w")]
+        else:
+            raise ValueError(f"{cfg.name}: layer {l} has mixer {sp.mixer!r}, which is not part of this family")
+        specs += [(p + "rg1", (W, W), "w"), (p + "rg1.b", (W,), "bias")]
+        if sp.ff:
+            specs.append((p + "norm2", (W,), "one"))
+            if sp.ff_kind == "moe":
+                for e in range(sp.experts):
+                    specs += [(f"{p}mlp.e{e}.up", (sp.expert_ff, W), "w"), (f"{p}mlp.e{e}.down", (W, sp.expert_ff), "w")]
+                n = sp.experts + sp.identity
+                specs += [(p + "mlp.router", (n, W), "w"), (p + "mlp.correction", (n,), "corr")]
+            else:
+                specs += [(p + "mlp.gate", (sp.ff, W), "w"), (p + "mlp.up", (sp.ff, W), "w"), (p + "mlp.down", (W, sp.ff), "w")]
+            specs += [(p + "rg2", (W, W), "w"), (p + "rg2.b", (W,), "bias")]
+    if last:
+        specs += [("final.norm", (W,), "one"), ("head", (cfg.vocab_size, W), "w")]
+    return specs
+
+
 def hybrid_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
     """tensor list of a hybrid family (configs with per-layer mixer specs)"""
-    fn = repudra_tensor_specs if cfg.family == "repudra" else kepovik_tensor_specs
+    fn = {"repudra": repudra_tensor_specs, "lonulix": lonulix_tensor_specs}.get(cfg.family, kepovik_tensor_specs)
     return fn(cfg, layers, first, last)
 
 
@@ -157,7 +196,7 @@ def _init_random_hybrid(cfg: ModelConfig, layers, first, last, device, dtype, se
     for name, shape, kind in hybrid_tensor_specs(cfg, layers, first, last):
         if kind == "w":
             std = 1.0 if name in ("embed", "bigram") else shape[-1] ** -0.5
-            if cfg.family == "repudra" and name == "embed":
+            if cfg.family in ("repudra", "lonulix") and name == "embed":
                 std = 1.0 / max(cfg.embed_scale, 1e-6)        # the scaled embedding has unit variance
             t[name] = _randn(name, shape, std, seed, device, dtype)
             continue
@@ -165,6 +204,10 @@ def _init_random_hybrid(cfg: ModelConfig, layers, first, last, device, dtype, se
             t[name] = _randn(name, shape, shape[-1] ** -0.5, seed, device, dtype)
             continue
         noise = _randn(name, shape, 0.1 if kind != "bias" else 0.5, seed, device, torch.float32)
+        if kind == "frac":
+            noise = torch.sigmoid(15.0 * noise)
+        elif kind == "corr":
+            noise = noise / shape[0]
         if kind == "small":
             noise = noise + 0.5
         elif kind == "neg":
