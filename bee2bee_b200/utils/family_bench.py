@@ -1,6 +1,7 @@
 """Side-by-side throughput of two model families at equal size (``bench.py --families``): the hybrid Kepovik graph
 next to the closest uniform decoder (Llama), or (``--family repudra``) the parallel-block Repudra graph next to the
-closest hybrid (Kepovik); random weights, layer shapes of real models.
+closest hybrid (Kepovik), or (``--family lonulix``) the post-norm Lonulix graph next to Repudra (the other family whose
+attention and recurrences run on the kernels of ``csrc/seqmix.cu``); random weights, layer shapes of real models.
 
 Per width it reports (1) prefill and decode tokens/s through the same ``GpuRunner`` calls that serving uses (chunked
 graph prefill, CUDA-graph decode steps), timed with CUDA events, and (2) a per-kernel breakdown of one eager prefill
@@ -63,6 +64,40 @@ def repudra_sized(width: int, vocab: int = 32000) -> ModelConfig:
                        max_position=1 << 30, norm="rms", norm_eps=1e-5, act="xielu", glu=False, rope_theta=0.0,
                        embed_scale=width ** 0.5, final_softcap=30.0, layer_specs=specs, block_layout="parallel",
                        scalar_norm=True, layer_scale=True)
+
+
+def lonulix_sized(width: int, vocab: int = 32000) -> ModelConfig:
+    """six post-norm layers: HGRN2 (128-wide heads) + gated feed-forward, latent attention (window 1024) + routed experts,
+    HGRN2 + gated feed-forward, latent attention over all keys + routed experts, HGRN2, latent attention (window 1024).
+    Latent attention: width / 128 heads of 64 plain + 32 rotated query/key channels and 128 value channels over a cached
+    latent of 96 channels (cache row: 128 channels per token for all heads together), query latent width / 2.  Experts:
+    8 of width / 2 hidden channels in 2 groups (1 kept) beside 2 identity experts, 2 per token.  The layer matrices hold
+    about 52 width^2 parameters, as ``repudra_sized(width)`` and ``kepovik_sized(width)`` do."""
+    H = width // 128
+    ff = max(128, (3 * width // 2) // 128 * 128)
+
+    def latt(window):
+        return LayerSpec(mixer="latent_attention", heads=H, kv_heads=1, dim=64, vdim=128, scale=96 ** -0.5, window=window,
+                         rot=RotarySpec(dims=32, base=10000.0), q_rank=width // 2, kv_rank=96, rot_dim=32)
+
+    def hgrn():
+        return LayerSpec(mixer="hgrn2", heads=H, kv_heads=H, dim=128, vdim=128)
+
+    def dense(sp):
+        sp.ff = ff
+        return sp
+
+    def routed(sp):
+        sp.ff_kind, sp.experts, sp.expert_ff, sp.top, sp.identity = "moe", 8, width // 2, 2, 2
+        sp.route_groups, sp.route_keep, sp.route_scale, sp.ff = 2, 1, 2.0, 8 * (width // 2)
+        return sp
+
+    specs = (dense(hgrn()), routed(latt(1024)), dense(hgrn()), routed(latt(0)), hgrn(), latt(1024))
+    return ModelConfig(name=f"mini-lonulix-{width}", family="lonulix", vocab_size=vocab, hidden_size=width,
+                       n_layers=len(specs), n_heads=H, n_kv_heads=1, head_dim=128, ffn_size=max(sp.ff for sp in specs),
+                       max_position=1 << 30, norm="rms", norm_eps=1e-6, act="silu", glu=True, rope_theta=0.0,
+                       embed_scale=2.0, layer_specs=specs, block_layout="post_norm", norm_groups=4, skip_scale=2.0,
+                       gated_residual=True)
 
 
 def llama_sized(width: int, layer_params: int, n_layers: int = 4, vocab: int = 32000) -> ModelConfig:
@@ -205,6 +240,21 @@ def cost(name: str, a, hint: Dict):
     if name == "scan_post":
         H, dv = a[8], a[9]
         return 0.0, T * H * dv * (4 + 4 + 2), False
+    if name == "post_norm_join":
+        W = a[0].shape[-1]
+        rows = a[2]
+        gathered = a[1] is not None
+        terms = (1 if a[3] is not None else 0) + (1 if a[4] is not None else 0)
+        return 0.0, rows * W * 4 * ((1 if gathered else 2) + terms) + rows * W * a[12].element_size(), False
+    if name == "latent_prep":
+        return 0.0, T * (a[2] + a[4] + a[5]) * 4 + T * a[2] * a[12].element_size() + T * (a[4] + a[5]) * a[13].element_size(), False
+    if name == "rot_heads":
+        return 0.0, 2 * T * a[3] * a[4] * 4, False
+    if name == "moe_route":
+        return 0.0, T * (a[2].numel() + a[3] + 1) * 4, False
+    if name == "gated_cols":
+        n = a[6]
+        return 0.0, T * n * ((4 if a[3] is not None else 8) + a[5].element_size()), False
     if name in ("rmsnorm", "layernorm", "add"):
         return 0.0, 3 * _nb(a[0]), False
     if name == "embed":
@@ -334,7 +384,10 @@ def run(widths, prompt_len=2048, batch=32, steps=32, warmup=3, ctx=512, device="
     out = []
     for w in widths:
         kep = kepovik_sized(w)
-        pair = (repudra_sized(w), kep) if family == "repudra" else (kep, llama_sized(w, layer_params(kep)))
+        if family == "lonulix":
+            pair = (lonulix_sized(w), repudra_sized(w))
+        else:
+            pair = (repudra_sized(w), kep) if family == "repudra" else (kep, llama_sized(w, layer_params(kep)))
         for cfg in pair:
             out.append(bench_family(cfg, torch.device(device), prompt_len, batch, steps, warmup, ctx, peaks))
     return out
