@@ -17,8 +17,8 @@ from typing import Dict, List, Optional, Tuple
 
 @dataclass
 class RotarySpec:
-    """Rotary positions on the first ``dims`` channels of every head, channel 2i paired with 2i+1, frequency of pair i
-    ``base ** (-2i / dims)``.  ``factor`` > 0: YaRN -- pairs that turn fewer than ``slow`` times within ``original``
+    """Rotary positions on the first ``dims`` channels of every head, channel 2i paired with 2i+1 (``half``: channel i
+    paired with i + dims/2), frequency of pair i ``base ** (-2i / dims)``.  ``factor`` > 0: YaRN -- pairs that turn fewer than ``slow`` times within ``original``
     positions are slowed by ``factor``, pairs that turn more than ``fast`` times keep their frequency, a linear ramp in
     between; cos and sin are multiplied by ``0.1 ln(factor) + 1``."""
     dims: int = 0
@@ -27,6 +27,7 @@ class RotarySpec:
     original: int = 0
     fast: float = 32.0
     slow: float = 1.0
+    half: bool = False
 
     def frequencies(self) -> List[float]:
         """angle per position of every rotated pair (float64 arithmetic; the kernels round them to fp32)"""
@@ -68,7 +69,15 @@ class LayerSpec:
     ``ff_kind`` = "moe": ``experts`` small feed-forwards (``expert_ff`` wide, no gate) of which a token uses ``top``,
     chosen by a softmax router; consecutive experts are bundled into ``route_groups`` equal groups and only the
     ``route_keep`` best-scoring groups may supply experts; the last
-    ``identity`` outputs of the router bypass the experts (they hand the input through); weights are renormalised and multiplied by ``route_scale``."""
+    ``identity`` outputs of the router bypass the experts (they hand the input through); weights are renormalised and multiplied by ``route_scale``.
+    ``route_kind`` = "logit_topk": the ``top`` largest router logits are chosen and weighted by the softmax over the chosen
+    logits alone; ``expert_gated``: an expert is ``down(silu(gate h) * up h)``; ``shared_ff`` > 0: one more expert of that
+    width runs for every token with weight 1.
+    Softmax attention options: ``qk_norm`` "whole" (RMS norm over the whole q / k projection) or "head" (per head, one
+    weight vector shared by the heads); ``v_norm`` (values normed per head); ``softcap`` > 0 (``score <- cap tanh(score /
+    cap)``); ``keep_first`` (with ``window``: the first keys stay visible); ``sink`` (a learned score per head joins the
+    softmax denominator).  Latent attention: ``q_rank`` 0 = queries come straight from the layer input; ``out_gate``: the
+    concatenated heads are multiplied by ``sigmoid(W_g h)`` in front of the output projection."""
     mixer: str = "attention"
     heads: int = 1
     kv_heads: int = 1
@@ -95,6 +104,15 @@ class LayerSpec:
     route_keep: int = 1
     identity: int = 0                # moe: router outputs that pass the feed-forward input through unchanged
     route_scale: float = 1.0
+    route_kind: str = "softmax_corrected"
+    expert_gated: bool = False
+    shared_ff: int = 0
+    qk_norm: str = "whole"
+    v_norm: bool = True
+    softcap: float = 0.0
+    keep_first: int = 0
+    sink: bool = False
+    out_gate: bool = False
 
     @property
     def leaves(self) -> Tuple["LayerSpec", ...]:
@@ -104,7 +122,7 @@ class LayerSpec:
 @dataclass
 class ModelConfig:
     name: str = "tiny-llama"
-    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik | repudra | lonulix
+    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik | repudra | lonulix | fisopel
     vocab_size: int = 512
     hidden_size: int = 256
     n_layers: int = 2
@@ -144,6 +162,13 @@ class ModelConfig:
     gated_residual: bool = False     # post_norm: sublayer results are multiplied by sigmoid(W x + b) before the sum
     scalar_norm: bool = False        # block / model norms have ONE gain (a single number) instead of one per coordinate
     layer_scale: bool = False        # sublayer outputs are multiplied coordinate-wise by learned vectors before the join
+    ff_norm: bool = False            # parallel blocks: the feed-forward reads a norm of its own (norm2) of the same residual
+    # layers loop_start .. loop_stop-1 run loop_times times in a row with the same weights (a cache per pass); with loop_in, the
+    # residual entering each pass is replaced by W_in [x ; embedding output]
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    loop_in: bool = False
 
     # ------------------------------------------------------------------ derived
     @property
@@ -156,6 +181,16 @@ class ModelConfig:
         return any(leaf.mixer not in ("attention", "softmax_attention", "latent_attention")
                    for sp in self.layer_specs for leaf in sp.leaves) \
             or self.pair_buckets > 0
+
+    def layer_runs(self) -> List[Tuple[int, int, bool]]:
+        """(layer, pass, first layer of a pass of the loop) in execution order"""
+        n = self.n_layers
+        if self.loop_stop <= self.loop_start:
+            return [(l, 0, False) for l in range(n)]
+        runs = [(l, 0, False) for l in range(self.loop_start)]
+        for p in range(max(1, self.loop_times)):
+            runs += [(l, p, l == self.loop_start) for l in range(self.loop_start, self.loop_stop)]
+        return runs + [(l, 0, False) for l in range(self.loop_stop, n)]
 
     @property
     def q_dim(self) -> int:
@@ -404,7 +439,96 @@ class ModelConfig:
                 "vocab": self.vocab_size, "width": self.hidden_size}
 
     @staticmethod
+    def from_fisopel_dict(d: Dict, name: str = "") -> "ModelConfig":
+        """``config.json`` of a Fisopel checkpoint: ``layers`` lists {type, mixer sizes, mlp | null}; types ``attention``
+        (grouped heads, per-head q / k norm, capped scores, window with kept first keys, sink) and ``latent_attention``
+        (gated); ``mlp.kind`` ``moe`` (gated silu experts beside a shared one); ``loop`` repeats a range of layers."""
+        who = name or "fisopel"
+        specs = []
+        for lay in d["layers"]:
+            m, mlp, kind = lay.get("mixer") or {}, lay.get("mlp"), lay["type"]
+            heads, dim = int(m["heads"]), int(m["dim"])
+            vdim = int(m.get("vdim", dim))
+            if kind == "attention":
+                mask = m.get("mask") or {}
+                sp = LayerSpec(mixer="softmax_attention", heads=heads, kv_heads=int(m.get("kv_heads", heads)), dim=dim,
+                               vdim=vdim, scale=float(m.get("scale", dim ** -0.5)), window=int(mask.get("size", 0) or 0),
+                               keep_first=int(mask.get("keep_first", 0) or 0), softcap=float(m.get("softcap", 0.0) or 0.0),
+                               qk_norm="head", v_norm=False, sink=True)
+                if sp.heads % sp.kv_heads:
+                    raise ValueError(f"{who}: {sp.heads} heads cannot share {sp.kv_heads} key heads")
+            elif kind == "latent_attention":
+                rot_dim = int(m.get("rot_dim", 0))
+                r = m.get("rot") or {}
+                sc = r.get("scaling") or {}
+                rot = RotarySpec(dims=int(r.get("dims", rot_dim)), base=float(r.get("base", 10000.0)),
+                                 factor=float(sc.get("factor", 0.0)), original=int(sc.get("original", 0)),
+                                 fast=float(sc.get("fast", 32.0)), slow=float(sc.get("slow", 1.0)), half=True) if rot_dim else None
+                if rot is not None and (rot.dims % 2 or rot.dims > rot_dim):
+                    raise ValueError(f"{who}: rotary dims {rot.dims} do not fit {rot_dim} rotated channels")
+                sp = LayerSpec(mixer=kind, heads=heads, kv_heads=1, dim=dim, vdim=vdim,
+                               scale=float(m.get("scale", (dim + rot_dim) ** -0.5)), rot=rot, q_rank=0,
+                               kv_rank=int(m["kv_rank"]), rot_dim=rot_dim, out_gate=True)
+            else:
+                raise ValueError(f"{who}: unknown layer type {kind!r}")
+            if mlp:
+                if mlp.get("kind", "moe") != "moe":
+                    raise ValueError(f"{who}: feed-forward kind {mlp.get('kind')!r} is not implemented")
+                r = mlp["router"]
+                sp.ff_kind, sp.expert_ff, sp.experts, sp.top = "moe", int(mlp["expert"]["ff"]), int(r["experts"]), int(r["top"])
+                sp.route_kind, sp.expert_gated = "logit_topk", True
+                sp.shared_ff = int((mlp.get("shared") or {}).get("ff", 0))
+                sp.ff = sp.experts * sp.expert_ff + sp.shared_ff
+                if not 0 < sp.top <= sp.experts:
+                    raise ValueError(f"{who}: {sp.top} of {sp.experts} experts cannot be chosen")
+            specs.append(sp)
+        width, n = int(d["width"]), len(specs)
+        loop = d.get("loop") or {}
+        start, stop = int(loop.get("start", 0)), int(loop.get("stop", 0))
+        if loop and not (0 <= start < stop <= n and int(loop.get("times", 1)) >= 1):
+            raise ValueError(f"{who}: loop {loop!r} does not fit {n} layers")
+        att = [sp for sp in specs if sp.mixer == "softmax_attention"] or specs
+        return ModelConfig(
+            name=name or "fisopel", family="fisopel", vocab_size=int(d["vocab"]), hidden_size=width, n_layers=n,
+            n_heads=max(sp.heads for sp in att), n_kv_heads=max(sp.kv_heads for sp in att),
+            head_dim=max(sp.dim for sp in att), ffn_size=max([sp.ff for sp in specs] + [0]), max_position=1 << 30,
+            norm="rms", norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)), act="silu", glu=True, rope_theta=0.0,
+            tie_embeddings=True, embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)),
+            layer_specs=tuple(specs), streams=0, block_layout="parallel", ff_norm=True, loop_start=start if loop else 0,
+            loop_stop=stop if loop else 0, loop_times=int(loop.get("times", 1)), loop_in=bool(loop))
+
+    def to_fisopel_dict(self) -> Dict:
+        layers = []
+        for sp in self.layer_specs:
+            if sp.mixer == "softmax_attention":
+                m = {"dim": sp.dim, "heads": sp.heads, "kv_heads": sp.kv_heads, "scale": sp.scale, "softcap": sp.softcap,
+                     "vdim": sp.vdim}
+                if sp.window:
+                    m["mask"] = {"keep_first": sp.keep_first, "size": sp.window}
+            else:
+                m = {"dim": sp.dim, "heads": sp.heads, "kv_rank": sp.kv_rank, "rot_dim": sp.rot_dim, "scale": sp.scale,
+                     "vdim": sp.vdim}
+                if sp.rot is not None:
+                    m["rot"] = {"base": sp.rot.base, "dims": sp.rot.dims}
+                    if sp.rot.factor > 0:
+                        m["rot"]["scaling"] = {"factor": sp.rot.factor, "fast": sp.rot.fast,
+                                               "original": sp.rot.original, "slow": sp.rot.slow}
+            mlp = None
+            if sp.ff:
+                mlp = {"expert": {"ff": sp.expert_ff}, "kind": "moe", "router": {"experts": sp.experts, "top": sp.top}}
+                if sp.shared_ff:
+                    mlp["shared"] = {"ff": sp.shared_ff}
+            layers.append({"type": "attention" if sp.mixer == "softmax_attention" else sp.mixer, "mixer": m, "mlp": mlp})
+        d = {"architecture": "Fisopel", "embedding": {"scale": self.embed_scale}, "layers": layers,
+             "norm": {"eps": self.norm_eps}, "vocab": self.vocab_size, "width": self.hidden_size}
+        if self.loop_in:
+            d["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
+        return d
+
+    @staticmethod
     def from_hf_dict(d: Dict, name: str = "") -> "ModelConfig":
+        if str(d.get("architecture", "")).lower() == "fisopel":
+            return ModelConfig.from_fisopel_dict(d, name)
         if str(d.get("architecture", "")).lower() == "lonulix":
             return ModelConfig.from_lonulix_dict(d, name)
         if str(d.get("architecture", "")).lower() == "kepovik":
@@ -458,6 +582,8 @@ class ModelConfig:
             return self.to_repudra_dict()
         if self.family == "lonulix":
             return self.to_lonulix_dict()
+        if self.family == "fisopel":
+            return self.to_fisopel_dict()
         if self.family == "gpt2":
             return {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "vocab_size": self.vocab_size,
                     "n_embd": self.hidden_size, "n_layer": self.n_layers, "n_head": self.n_heads,
@@ -620,6 +746,43 @@ def _lonulix(name, width, vocab, layers, groups=2, alpha=2.0, embed_scale=2.0):
 PRESETS["tiny-lonulix"] = _lonulix("tiny-lonulix", 128, 512, [
     ("latent_attention", 4, 16, 8, 24, 48, 40, 48, (6, 64, 2, 4, 2, 2, 1.5)), ("hgrn2", 2, 32, 48, 192),
     ("hgrn2", 4, 16, 16, 0), ("latent_attention", 2, 32, 16, 32, 64, 32, 0, 256)])
+
+
+def _fisopel(name, width, vocab, layers, loop=None, embed_scale=2.0):
+    """layers: ("attention", H, G, dim, vdim, window, keep_first, softcap, mlp) | ("latent_attention", H, dim, rot_dim, vdim,
+    kv_rank, yarn factor, mlp); mlp: 0 (none) | (experts, expert_ff, top, shared_ff); loop: (start, stop, times)"""
+    specs = []
+    for lay in layers:
+        if lay[0] == "attention":
+            _, h, g, d, v, win, keep, cap, mlp = lay
+            sp = LayerSpec(mixer="softmax_attention", heads=h, kv_heads=g, dim=d, vdim=v, scale=d ** -0.5, window=win,
+                           keep_first=keep, softcap=cap, qk_norm="head", v_norm=False, sink=True)
+        else:
+            _, h, d, r, v, kr, fac, mlp = lay
+            rot = RotarySpec(dims=r, base=10000.0, factor=fac, original=64 if fac > 0 else 0, half=True) if r else None
+            sp = LayerSpec(mixer="latent_attention", heads=h, kv_heads=1, dim=d, vdim=v, scale=(d + r) ** -0.5, rot=rot,
+                           q_rank=0, kv_rank=kr, rot_dim=r, out_gate=True)
+        if mlp:
+            e, eff, top, sh = mlp
+            sp.ff_kind, sp.experts, sp.expert_ff, sp.top, sp.shared_ff = "moe", e, eff, top, sh
+            sp.route_kind, sp.expert_gated, sp.ff = "logit_topk", True, e * eff + sh
+        specs.append(sp)
+    att = [sp for sp in specs if sp.mixer == "softmax_attention"] or specs
+    lp = loop or (0, 0, 1)
+    return ModelConfig(name=name, family="fisopel", vocab_size=vocab, hidden_size=width, n_layers=len(specs),
+                       n_heads=max(sp.heads for sp in att), n_kv_heads=max(sp.kv_heads for sp in att),
+                       head_dim=max(sp.dim for sp in att), ffn_size=max(sp.ff for sp in specs), max_position=1 << 30,
+                       norm="rms", norm_eps=1e-5, act="silu", glu=True, rope_theta=0.0, tie_embeddings=True,
+                       embed_scale=embed_scale, layer_specs=tuple(specs), block_layout="parallel", ff_norm=True,
+                       loop_start=lp[0], loop_stop=lp[1], loop_times=lp[2], loop_in=loop is not None,
+                       eos_token_id=-1, bos_token_id=-1)
+
+
+# looped parallel-block test preset: windowed attention with kept first keys and a sink + routed experts, gated latent
+# attention (YaRN rotary part) + routed experts, both run twice; then latent attention without a feed-forward
+PRESETS["tiny-fisopel"] = _fisopel("tiny-fisopel", 128, 512, [
+    ("attention", 4, 2, 32, 16, 40, 6, 30.0, (6, 32, 2, 48)), ("latent_attention", 3, 16, 16, 24, 48, 4.0, (5, 32, 3, 0)),
+    ("latent_attention", 2, 32, 8, 32, 40, 0.0, 0)], loop=(0, 2, 2))
 PRESETS["tiny-gpt2"].vocab_size = 384
 PRESETS["tiny-gpt2"].eos_token_id = 1
 PRESETS["tiny-gpt2"].bos_token_id = 0

@@ -18,6 +18,13 @@ the paged cache holds ``[rotated part | latent]`` rows only) and HGRN2 (keyless 
 bound, and its complement as the write strength).  Feed-forward: gated silu, or routed gelu experts (softmax router, selection-only correction,
 group-limited top-k, identity experts).
 
+Family ``fisopel``: parallel blocks with a norm each for the mixer and the feed-forward (``x <- x + mixer(norm1 x) +
+ff(norm2 x)``), a range of layers that runs several times with the same weights (a cache per pass; the residual entering a
+pass is ``W_in [x ; embedding output]``), logits from the embedding table.  Mixers: softmax attention with a per-head q / k
+norm, capped scores, a window that keeps the first keys in sight and a sink in the denominator; gated latent attention (keys
+absorbed into the queries, values up-projected per head behind the attention, rotary part in the half-split pairing with
+YaRN frequencies).  Feed-forward: gated silu experts chosen by their router logits beside a shared expert.
+
 Same interface as ``native.NativePiece`` (the runner drives both through ``forward(BatchMeta)``): a flat batch of spans
 (prompt portions of any length beside single decoded tokens), physical KV slots and block tables from the page allocator,
 logits for the rows named by ``last_idx``.  What is new here and lives next to the shared machinery:
@@ -65,6 +72,7 @@ class _Mix:
     join_w: Optional[torch.Tensor] = None    # coordinate-wise weight of its output in the residual join
     join_norm: bool = False                  # its output is divided by its root mean square over the width first
     amp: float = 1.0                         # rotary amplitude
+    w_uv: Optional[torch.Tensor] = None      # latent attention with an output gate: [heads, vdim, kv_rank] value up-projections
 
 
 @dataclass
@@ -78,6 +86,7 @@ class _Layer:
     w_up: Optional[torch.Tensor] = None
     w_down: Optional[torch.Tensor] = None
     w_glu: Optional[torch.Tensor] = None   # post-norm dense feed-forward, bf16: [gate | up] interleaved for the gated GEMM epilogue
+    ff_off: Dict[str, int] = field(default_factory=dict)    # routed experts: columns of router / gate block / up block
     mix: tuple = ()                     # parallel blocks: the mixers that read the layer's input side by side
     act_params: tuple = (0.0, 0.0)      # xIELU: softplus(p), 1/2 + softplus(q)
 
@@ -164,7 +173,10 @@ class HybridPiece:
         self.embed = tensors["embed"].to(device=dev, dtype=dtype).contiguous()
         self.pair = tensors["bigram"].to(device=dev, dtype=dtype).contiguous() if cfg.pair_buckets else None
         self.final_norm = vec("final.norm").reshape(-1)
-        self.w_head = mat("head")
+        self.w_head = mat("embed" if cfg.tie_embeddings else "head")
+        self.w_loop = mat("loop.in") if cfg.loop_in else None       # [x ; embedding output] -> the residual entering a pass
+        self.runs = [r for r in cfg.layer_runs() if r[0] in self.L]  # (layer, pass, first of a pass) in execution order
+        self._pass = 0
         self.vocab_pad = self.w_head.shape[0]
 
         # ---- per-sequence state (indexed by batch slot) and the paged KV cache of the attention layers
@@ -178,8 +190,10 @@ class HybridPiece:
         for l in self.layers:
             sp = cfg.layer_specs[l]
             if self.parallel_blocks or self.post_norm:
-                for mx in self.L[l].mix:
-                    self._alloc_mixer_state(mx, num_pages)
+                for self._pass in sorted({p for ll, p, _ in self.runs if ll == l}):     # a cache / state per pass of a looped layer
+                    for mx in self.L[l].mix:
+                        self._alloc_mixer_state(mx, num_pages)
+                self._pass = 0
                 continue
             if sp.mixer == "attention":
                 self.k_cache[l] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.dim), device=dev, dtype=dtype)
@@ -190,6 +204,7 @@ class HybridPiece:
         self.streams = torch.zeros((max_tokens, self.ns, W), device=dev, dtype=f32)
         self._bufs: Dict[tuple, torch.Tensor] = {}
         self.h = self._buf("h", dtype, self.Wp)
+        self.h2 = self._buf("h2", dtype, self.Wp) if cfg.ff_norm else None
         self.last_x = torch.zeros((self.max_out_rows, self.Wp), device=dev, dtype=dtype)
         self.logits = torch.zeros((self.max_out_rows, self.vocab_pad), device=dev, dtype=f32)
         self._ones = torch.ones(self.ns, device=dev, dtype=f32)
@@ -203,13 +218,19 @@ class HybridPiece:
             b = self._bufs[key] = torch.zeros((self.max_tokens, width), device=self.device, dtype=dtype)
         return b
 
+    def _key(self, mx: _Mix) -> str:
+        """name of the cache / state of mixer ``mx`` in the current pass of the loop (pass 0: the mixer's own key)"""
+        return mx.key if self._pass == 0 else f"{mx.key}@{self._pass}"
+
     def _matrices(self):
+        if self.w_loop is not None:
+            yield self.w_loop
         for L in self.L.values():
             for t in (L.w_cat, L.w_o, L.w2, L.w_up, L.w_down, L.w_glu):
                 if t is not None:
                     yield t
             for mx in L.mix:
-                for t in (mx.w_o, mx.w2):
+                for t in (mx.w_o, mx.w2, mx.w_uv):
                     if t is not None:
                         yield t
 
@@ -235,10 +256,14 @@ class HybridPiece:
                     n += 4 + (1 if L.spec.ff_kind == "moe" else 0)
             return n
         if self.parallel_blocks:
-            per = {"softmax_attention": 3, "mlstm": 4, "gla": 5, "channel_delta": 7}
+            per = {"softmax_attention": 3, "mlstm": 4, "gla": 5, "channel_delta": 7, "latent_attention": 5}
             n = 2 + (1 if self.caps_logits else 0)       # embedding, final join + norm (+ soft cap; head GEMM: the runner)
-            for L in self.L.values():
-                n += 2 + sum(per[mx.spec.mixer] for mx in L.mix) + (2 if L.spec.ff else 0)   # join + fused projection
+            n += 1 if self.w_loop is not None else 0     # copy of the embedding output
+            for l, _, first in self.runs:
+                L = self.L[l]
+                n += 2 + sum(per[mx.spec.mixer] for mx in L.mix)                             # join + fused projection
+                n += (4 if L.spec.ff_kind == "moe" else 2) if L.spec.ff else 0
+                n += 2 if (first and self.w_loop is not None) else 0
             return n
         n = 3          # embedding, final stream sum + norm, previous-token commit (+ the head GEMM counted by the runner)
         for L in self.L.values():
@@ -304,17 +329,28 @@ class HybridPiece:
         W = self.cfg.hidden_size
         L.f["norm1"] = vec(p + "norm1").reshape(-1)
         ls1 = vec(p + "ls1") if self.cfg.layer_scale else torch.ones(W, device=dev)
-        names, col, mixes = [], 0, []
+        col, mixes = 0, []
+        blocks = []                       # row blocks of the fused projection, in float64
         for j, leaf in enumerate(sp.leaves):
             q = p + "mix." + (("left.", "right.")[j] if sp.mixer == "parallel" else "")
             mx = _Mix(spec=leaf, key=f"{l}.{j}", idx=j)
-            for n in _PROJ[leaf.mixer]:
-                mx.off[n] = col
-                col += tensors[q + n].shape[0]
-                names.append(q + n)
+            if leaf.mixer == "latent_attention":
+                for n, w in self._latent_rows(mx, q, tensors):
+                    mx.off[n] = col
+                    col += w.shape[0]
+                    blocks.append(w)
+            else:
+                for n in _PROJ[leaf.mixer]:
+                    mx.off[n] = col
+                    col += tensors[q + n].shape[0]
+                    blocks.append(tensors[q + n].to(device=dev, dtype=torch.float64))
             mx.w_o = mat(q + "o")
-            if leaf.mixer == "softmax_attention":
+            if leaf.mixer == "latent_attention":
+                pass
+            elif leaf.mixer == "softmax_attention":
                 mx.f["q.norm"], mx.f["k.norm"] = vec(q + "q.norm"), vec(q + "k.norm")
+                if leaf.sink:
+                    mx.f["sink"] = vec(q + "sink")
                 rot = leaf.rot
                 freq = rot.frequencies() if rot is not None and rot.dims > 0 else [0.0]
                 mx.f["freq"] = torch.tensor(freq, dtype=torch.float64).to(device=dev, dtype=torch.float32)
@@ -339,35 +375,93 @@ class HybridPiece:
                 mx.join_w = (vec(q + "out") * ls1 / len(sp.leaves)).contiguous()
                 mx.join_norm = True
             else:
-                mx.join_w = ls1
+                mx.join_w = ls1 if self.cfg.layer_scale else None
             mixes.append(mx)
         L.mix = tuple(mixes)
-        w = torch.cat([tensors[n].to(device=dev, dtype=torch.float32) for n in names], 0)
-        L.w_cat = ops.pad_weight(w, 128, 64).to(self.dtype).contiguous()
+        L.w_cat = ops.pad_weight(torch.cat(blocks, 0).to(torch.float32), 128, 64).to(self.dtype).contiguous()
         if sp.ff:
+            if self.cfg.ff_norm:
+                L.f["norm2"] = vec(p + "norm2")
+            L.f["ls2"] = vec(p + "ls2") if self.cfg.layer_scale else None
+            if sp.ff_kind == "moe":
+                self._build_routed_ff(L, p, tensors)
+                return L
             L.w_up, L.w_down = mat(p + "mlp.up"), mat(p + "mlp.down", k_mult=128)
             a = vec(p + "mlp.act")
             L.act_params = (float(F.softplus(a[0])), float(0.5 + F.softplus(a[1])))
-            L.f["ls2"] = vec(p + "ls2") if self.cfg.layer_scale else torch.ones(W, device=dev)
+            if L.f["ls2"] is None:
+                L.f["ls2"] = torch.ones(W, device=dev)
         return L
+
+    def _latent_rows(self, mx: _Mix, q: str, tensors: Tensors):
+        """Row blocks (name, float64 matrix) that gated latent attention adds to the fused projection of its layer, and the
+        mixer's own tensors.  Served with the keys absorbed: ``q_h . (U_k,h c) = (U_k,h^T q_h) . c``, so per head the query
+        rows become ``[rotated part | U_k,h^T W_q,h]`` (``rot_dim + kv_rank`` channels) and attention runs over the cached
+        rows ``[rotated key part | latent]``.  The values cannot be folded into the output projection (the output gate
+        multiplies the concatenated heads in between): the per-head up-projections stay a tensor of their own.  Rotary
+        pairs stored half-split (channel i with i + dims/2) are interleaved here, on the query rows and on the key rows
+        alike, so that the kernels turn adjacent channels; the dot products do not notice."""
+        sp, dev, f64 = mx.spec, self.device, torch.float64
+        H, D, R, V, C = sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank
+        W = self.cfg.hidden_size
+        wq = tensors[q + "q"].to(device=dev, dtype=f64).view(H, D + R, W)
+        dkv = tensors[q + "dkv"].to(device=dev, dtype=f64)
+        uk = tensors[q + "uk"].to(device=dev, dtype=f64).view(H, D, C)
+        rd = sp.rot.dims if sp.rot is not None else 0
+        perm = torch.arange(R, device=dev)
+        if rd and sp.rot.half:
+            perm[:rd] = torch.arange(rd, device=dev).view(2, rd // 2).t().reshape(-1)       # new 2i <- i, new 2i+1 <- i + rd/2
+        qa = torch.cat([wq[:, D:][:, perm], torch.einsum("hdc,hdw->hcw", uk, wq[:, :D])], 1)     # [H, R + C, W]
+        kv = torch.cat([dkv[:C], dkv[C:][perm]], 0)
+        mx.f["dkv.norm"] = tensors[q + "dkv.norm"].to(device=dev, dtype=torch.float32).contiguous()
+        freq = sp.rot.frequencies() if rd else [0.0]
+        mx.f["freq"] = torch.tensor(freq, dtype=f64).to(device=dev, dtype=torch.float32)
+        mx.amp = sp.rot.amplitude if rd else 1.0
+        mx.w_uv = tensors[q + "uv"].to(device=dev, dtype=torch.float32).view(H, V, C).to(self.dtype).contiguous()
+        rows = [("qa", qa.reshape(H * (R + C), W)), ("dkv", kv)]
+        if sp.out_gate:
+            rows.append(("g", tensors[q + "g"].to(device=dev, dtype=f64)))
+        return rows
+
+    def _build_routed_ff(self, L: _Layer, p: str, tensors: Tensors) -> None:
+        """Gated experts chosen by their router logits, beside a shared expert: ONE up matrix ``[router | gate rows of
+        the shared expert and of every expert | their up rows]`` and ONE down matrix with the down-projections side by
+        side, so a token's weighted expert sum is a column scaling between two GEMMs (no sorting, no host)."""
+        sp, dev, f64 = L.spec, self.device, torch.float64
+        W = self.cfg.hidden_size
+        names = (["shared"] if sp.shared_ff else []) + [f"e{e}" for e in range(sp.experts)]
+
+        def t64(n):
+            return tensors[n].to(device=dev, dtype=f64)
+
+        router = t64(p + "mlp.router")
+        pad = router.new_zeros(((-router.shape[0]) % 4, W))          # the blocks behind it start at multiples of four
+        gates = torch.cat([t64(f"{p}mlp.{n}.gate") for n in names], 0)
+        ups = torch.cat([t64(f"{p}mlp.{n}.up") for n in names], 0)
+        n_r, n_h = router.shape[0] + pad.shape[0], gates.shape[0]
+        L.ff_off = {"router": 0, "gate": n_r, "up": n_r + n_h, "hidden": n_h}
+        L.w_up = ops.pad_weight(torch.cat([router, pad, gates, ups], 0).to(torch.float32), 128, 64).to(self.dtype).contiguous()
+        down = torch.cat([t64(f"{p}mlp.{n}.down") for n in names], 1)
+        L.w_down = ops.pad_weight(down.to(torch.float32), 128, 64).to(self.dtype).contiguous()
 
     def _alloc_mixer_state(self, mx: _Mix, num_pages: int) -> None:
         sp, dev, f32 = mx.spec, self.device, torch.float32
+        key = self._key(mx)
         if sp.mixer == "latent_attention":      # one row per token: [rotated key part | latent]; the values are its latent slice
-            self.k_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, 1, sp.rot_dim + sp.kv_rank), device=dev, dtype=self.dtype)
-            self.v_cache[mx.key] = self.k_cache[mx.key][..., sp.rot_dim:]
+            self.k_cache[key] = torch.zeros((num_pages, ops.PAGE, 1, sp.rot_dim + sp.kv_rank), device=dev, dtype=self.dtype)
+            self.v_cache[key] = self.k_cache[key][..., sp.rot_dim:]
             return
         if sp.mixer == "softmax_attention":
-            self.k_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.dim), device=dev, dtype=self.dtype)
-            self.v_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.vdim), device=dev, dtype=self.dtype)
+            self.k_cache[key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.dim), device=dev, dtype=self.dtype)
+            self.v_cache[key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.vdim), device=dev, dtype=self.dtype)
             return
-        self.state[mx.key] = torch.zeros((self.state_slots, sp.heads, sp.dim, sp.vdim), device=dev, dtype=f32)
+        self.state[key] = torch.zeros((self.state_slots, sp.heads, sp.dim, sp.vdim), device=dev, dtype=f32)
         if sp.mixer == "mlstm":
-            self.nstate[mx.key] = torch.zeros((self.state_slots, sp.heads, sp.dim), device=dev, dtype=f32)
-            self.mstate[mx.key] = torch.zeros((self.state_slots, sp.heads), device=dev, dtype=f32)
+            self.nstate[key] = torch.zeros((self.state_slots, sp.heads, sp.dim), device=dev, dtype=f32)
+            self.mstate[key] = torch.zeros((self.state_slots, sp.heads), device=dev, dtype=f32)
         elif sp.mixer == "channel_delta":
             ch, taps = mx.f["conv"].shape                 # the taps are the tensor's, whatever the config says
-            self.conv_tail[mx.key] = torch.zeros((self.state_slots, max(1, taps - 1), ch), device=dev, dtype=f32)
+            self.conv_tail[key] = torch.zeros((self.state_slots, max(1, taps - 1), ch), device=dev, dtype=f32)
 
     def _forward_parallel_blocks(self, m) -> torch.Tensor:
         """x = scale * embed;  per layer: h = norm(x), x += sum of the layer-scaled mixer / feed-forward outputs (all
@@ -380,9 +474,23 @@ class HybridPiece:
                       self.streams[:T], S, mq, scale=c.embed_scale)
         h = self.h[:T]
         pend: list = []
-        for l in self.layers:
+        hcat = None
+        if self.w_loop is not None:                  # operand of the loop's input matrix: [residual | embedding output]
+            hcat = self._buf("loop", self.dtype, self.w_loop.shape[1])[:T]
+            ops.act_cols(x, 0, hcat[:, W:], W, ops.COLS_COPY, T)
+        for l, self._pass, enters in self.runs:
             L = self.L[l]
-            ops.ls_join(x, m.q_start, m.q_len, S, mq, terms=pend, gamma=L.f["norm1"], eps=eps, h=h)
+            replace = False
+            if enters and hcat is not None:
+                # the outputs of the layer before join the residual, which becomes the left half of the operand; the
+                # product REPLACES the residual (joined by the norm kernel below)
+                ops.ls_join(x, m.q_start, m.q_len, S, mq, terms=pend, h=hcat[:, :W])
+                pend = [(ops.linear(self.w_loop, hcat, self._buf("yin", torch.float32, self.w_loop.shape[0])[:T]), None, False)]
+                replace = True
+            two = self.cfg.ff_norm and L.spec.ff > 0
+            hf = self.h2[:T] if two else h           # what the feed-forward reads
+            ops.ls_join(x, m.q_start, m.q_len, S, mq, terms=pend, gamma=L.f["norm1"], eps=eps, h=h, replace=replace,
+                        gamma2=L.f["norm2"] if two else None, h2=hf if two else None)
             proj = ops.linear(L.w_cat, h, self._buf("proj", torch.float32, L.w_cat.shape[0])[:T])
             pend = []
             joins = []
@@ -403,7 +511,7 @@ class HybridPiece:
 
             yff = None
             if L.spec.ff and self.overlap_ff:
-                yff = beside(self._side, lambda: self._ff(L, h, T))
+                yff = beside(self._side, lambda: self._ff(L, hf, T))
             for j, mx in enumerate(L.mix):
                 run = getattr(self, "_mix_" + mx.spec.mixer)
                 ybuf = self._buf(f"y{j}", torch.float32, mx.w_o.shape[0])[:T]
@@ -413,11 +521,12 @@ class HybridPiece:
                     y = run(mx, proj, m, ybuf)
                 pend.append((y, mx.join_w, mx.join_norm))
             if L.spec.ff:
-                pend.append((yff if yff is not None else self._ff(L, h, T), L.f["ls2"], False))
+                pend.append((yff if yff is not None else self._ff(L, hf, T), L.f["ls2"], False))
             for done in joins:
                 main.wait_event(done)
             if self.debug_layers is not None:
                 self.debug_layers.append(self._debug_join(x, pend, T))
+        self._pass = 0
         R = m.n_out or S
         rows = m.last_idx if m.last_idx is not None else m.q_start
         xl = self.last_x[:R]
@@ -547,25 +656,35 @@ class HybridPiece:
 
     def _mix_latent_attention(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
         sp, T = mx.spec, m.n_tokens
-        H, R, C, Q = sp.heads, sp.rot_dim, sp.kv_rank, sp.q_rank
-        kc, vc = self.k_cache[mx.key], self.v_cache[mx.key]
+        H, R, C, Q, V = sp.heads, sp.rot_dim, sp.kv_rank, sp.q_rank, sp.vdim
+        kc, vc = self.k_cache[self._key(mx)], self.v_cache[self._key(mx)]
         rdims = sp.rot.dims if sp.rot is not None else 0
-        cq = self._buf(f"cq{Q}", self.dtype, mx.w2.shape[1])[:T]
-        ops.latent_prep(proj, mx.off["dq"], Q, mx.off["dkv"], C, R, mx.f["dq.norm"], mx.f["dkv.norm"], mx.f["freq"], rdims,
-                        m.positions, m.slots, cq, kc, self.cfg.norm_eps, T)
-        qa = ops.linear(mx.w2, cq, self._buf("qa", torch.float32, mx.w2.shape[0])[:T])
-        q = self._buf("q0", torch.float32, H * (R + C))[:T]
-        ops.rot_heads(qa, 0, q, H, R + C, mx.f["freq"], rdims, m.positions, T, slots=m.slots)
-        ao = self._buf(f"mix0.{H * C}", self.dtype, mx.w_o.shape[1])[:T]
+        if Q > 0:                       # queries from a normed latent: a second GEMM gives the absorbed query rows
+            cq = self._buf(f"cq{Q}", self.dtype, mx.w2.shape[1])[:T]
+            ops.latent_prep(proj, mx.off["dq"], Q, mx.off["dkv"], C, R, mx.f["dq.norm"], mx.f["dkv.norm"], mx.f["freq"],
+                            rdims, m.positions, m.slots, cq, kc, self.cfg.norm_eps, T, amp=mx.amp)
+            qa, off_q = ops.linear(mx.w2, cq, self._buf("qa", torch.float32, mx.w2.shape[0])[:T]), 0
+        else:                           # queries straight from the layer input: their absorbed rows are in the fused projection
+            ops.latent_prep(proj, 0, 0, mx.off["dkv"], C, R, mx.f["dkv.norm"], mx.f["dkv.norm"], mx.f["freq"], rdims,
+                            m.positions, m.slots, self.h[:T], kc, self.cfg.norm_eps, T, amp=mx.amp)
+            qa, off_q = proj, mx.off["qa"]
+        q = self._buf(f"q{mx.idx}", torch.float32, H * (R + C))[:T]
+        ops.rot_heads(qa, off_q, q, H, R + C, mx.f["freq"], rdims, m.positions, T, slots=m.slots, amp=mx.amp)
+        ao = self._buf(f"mix{mx.idx}.{H * C}", self.dtype, ops.pad_to(H * C, 64))[:T]
         ops.softmax_attention(q, kc, vc, ao, m.block_table, m.q_start, m.q_len, m.kv_len, m.n_seqs, m.max_q, H, 1, R + C, C,
                               sp.window, sp.scale)
+        if mx.w_uv is not None:         # values per head behind the attention, times the output gate of the concatenated heads
+            go = self._buf(f"gate{mx.idx}.{H * V}", self.dtype, mx.w_o.shape[1])[:T]
+            ops.head_up_gate(ao, mx.w_uv, go, T, H, V, C, gate=proj if sp.out_gate else None,
+                             off_g=mx.off["g"] if sp.out_gate else 0)
+            ao = go
         return ops.linear(mx.w_o, ao, y)
 
     def _mix_hgrn2(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
         sp, T = mx.spec, m.n_tokens
         H, dk, dv = sp.heads, sp.dim, sp.vdim
         o = self._buf("o0", torch.float32, H * dv)[:T]
-        ops.lin_scan(ops.SCAN_HGRN2, proj, mx.off["q"], mx.off["q"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
+        ops.lin_scan(ops.SCAN_HGRN2, proj, mx.off["q"], mx.off["q"], proj, mx.off["v"], self.state[self._key(mx)], o, m.q_start,
                      m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, z=proj, off_z=mx.off["f"],
                      zbias=mx.f["f.b"], hparam=mx.f["lower"])
         do = self._buf(f"mix0.{H * dv}", self.dtype, mx.w_o.shape[1])[:T]
@@ -573,10 +692,26 @@ class HybridPiece:
         return ops.linear(mx.w_o, do, y)
 
     def _ff(self, L: _Layer, h: torch.Tensor, T: int) -> torch.Tensor:
-        """down(xIELU(up(h))): the activation is the epilogue of the up-projection"""
+        """down(xIELU(up(h))): the activation is the epilogue of the up-projection; routed experts: see ``_ff_routed``"""
+        if L.spec.ff_kind == "moe":
+            return self._ff_routed(L, h, T)
         hid = self._buf("ff", self.dtype, L.w_up.shape[0])[:T]
         ops.linear(L.w_up, h, hid, act=ops.ACT_XIELU, act_params=L.act_params)
         return ops.linear(L.w_down, hid, self._buf("yff", torch.float32, L.w_down.shape[0])[:T])
+
+    def _ff_routed(self, L: _Layer, h: torch.Tensor, T: int) -> torch.Tensor:
+        """shared expert + the ``top`` experts with the largest router logits, weighted by the softmax over those logits:
+        one GEMM (router logits, all gate rows, all up rows), the router, ``silu(gate) * up * weight`` per hidden column,
+        one GEMM over the down-projections side by side"""
+        sp, o, f32 = L.spec, L.ff_off, torch.float32
+        p2 = ops.linear(L.w_up, h, self._buf("proj2", f32, L.w_up.shape[0])[:T])
+        wt = self._buf("route", f32, max(1, sp.experts))[:T]
+        idw = self._buf("keep", f32, 1)[:T]
+        ops.moe_route(p2, o["router"], None, sp.experts, 1, 1, sp.top, 1.0, wt, idw, T)
+        hid = self._buf("ff", self.dtype, L.w_down.shape[1])[:T]
+        ops.gated_cols(p2, o["gate"], o["up"], hid, o["hidden"], ops.GATE_SILU, T, wt=wt, per=sp.expert_ff, both=True,
+                       lead=sp.shared_ff)
+        return ops.linear(L.w_down, hid, self._buf("yff", f32, L.w_down.shape[0])[:T])
 
     def _debug_join(self, x: torch.Tensor, terms, T: int) -> torch.Tensor:
         """the residual after the pending outputs have joined it (plain torch, tests only)"""
@@ -592,14 +727,19 @@ class HybridPiece:
     def _mix_softmax_attention(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
         sp, T = mx.spec, m.n_tokens
         H, G, D, V = sp.heads, sp.kv_heads, sp.dim, sp.vdim
-        kc, vc = self.k_cache[mx.key], self.v_cache[mx.key]
+        kc, vc = self.k_cache[self._key(mx)], self.v_cache[self._key(mx)]
         q = self._buf(f"q{mx.idx}", torch.float32, H * D)[:T]
-        ops.rot_attn_prep(proj, mx.off["q"], mx.off["k"], mx.off["v"], mx.f["q.norm"], mx.f["k.norm"], mx.f["freq"],
-                          sp.rot.dims if sp.rot is not None else 0, mx.amp, m.positions, m.slots, q, kc, vc, T, H, G, D, V,
+        if sp.qk_norm == "head":        # a norm per head (one weight vector for all heads), no rotation, values as they are
+            assert sp.rot is None and not sp.v_norm and mx.off["k"] == mx.off["q"] + H * D and mx.off["v"] == mx.off["k"] + G * D
+            ops.attn_prep(proj[:, mx.off["q"]:], mx.f["q.norm"], mx.f["k.norm"], m.slots, q, kc, vc, T, H, G, D, V,
                           self.cfg.norm_eps)
+        else:
+            ops.rot_attn_prep(proj, mx.off["q"], mx.off["k"], mx.off["v"], mx.f["q.norm"], mx.f["k.norm"], mx.f["freq"],
+                              sp.rot.dims if sp.rot is not None else 0, mx.amp, m.positions, m.slots, q, kc, vc, T, H, G, D,
+                              V, self.cfg.norm_eps)
         ao = self._buf(f"mix{mx.idx}.{H * V}", self.dtype, mx.w_o.shape[1])[:T]
         ops.softmax_attention(q, kc, vc, ao, m.block_table, m.q_start, m.q_len, m.kv_len, m.n_seqs, m.max_q, H, G, D, V,
-                              sp.window, sp.scale)
+                              sp.window, sp.scale, softcap=sp.softcap, keep_first=sp.keep_first, sink=mx.f.get("sink"))
         return ops.linear(mx.w_o, ao, y)
 
     def _scan_out(self, mx: _Mix, o, gate, off_g, act, aux, m, y) -> torch.Tensor:
@@ -614,10 +754,10 @@ class HybridPiece:
         qs = dk ** -0.5
         aux = self._buf(f"aux{mx.idx}", torch.float32, 4 * H)[:T]
         ops.mlstm_gates(proj, mx.off["q"], mx.off["k"], mx.off["i"], mx.off["f"], mx.f["i.b"], mx.f["f.b"], sp.gate_cap, qs,
-                        self.nstate[mx.key], self.mstate[mx.key], aux, m.q_start, m.q_len, m.kv_len, m.seq_slot, m.n_seqs,
+                        self.nstate[self._key(mx)], self.mstate[self._key(mx)], aux, m.q_start, m.q_len, m.kv_len, m.seq_slot, m.n_seqs,
                         H, dk)
         o = self._buf(f"o{mx.idx}", torch.float32, H * dv)[:T]
-        ops.lin_scan(ops.SCAN_MLSTM, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
+        ops.lin_scan(ops.SCAN_MLSTM, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[self._key(mx)], o, m.q_start,
                      m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, aux=aux, qscale=qs)
         return self._scan_out(mx, o, proj, mx.off["g"], 0, aux, m, y)
 
@@ -632,7 +772,7 @@ class HybridPiece:
         H, dk, dv = sp.heads, sp.dim, sp.vdim
         z = self._low_rank(mx, proj, mx.off["a1"], T)
         o = self._buf(f"o{mx.idx}", torch.float32, H * dv)[:T]
-        ops.lin_scan(ops.SCAN_GLA, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
+        ops.lin_scan(ops.SCAN_GLA, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[self._key(mx)], o, m.q_start,
                      m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, z=z, zbias=mx.f["zbias"],
                      qscale=dk ** -0.5, inv_tau=1.0 / sp.tau)
         return self._scan_out(mx, o, proj, mx.off["g"], 1, None, m, y)
@@ -642,11 +782,11 @@ class HybridPiece:
         H, G, dk, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
         cw = mx.f["conv"]
         conv = self._buf(f"conv{mx.idx}", torch.float32, cw.shape[0])[:T]
-        ops.short_conv(proj, mx.off["q"], cw, self.conv_tail[mx.key], conv, m.q_start, m.q_len, m.kv_len, m.seq_slot,
+        ops.short_conv(proj, mx.off["q"], cw, self.conv_tail[self._key(mx)], conv, m.q_start, m.q_len, m.kv_len, m.seq_slot,
                        m.n_seqs, m.max_q)
         z = self._low_rank(mx, proj, mx.off["a1"], T)           # [decay steps (H * dk) | output gate (H * dv)]
         o = self._buf(f"o{mx.idx}", torch.float32, H * dv)[:T]
-        ops.lin_scan(ops.SCAN_DELTA, conv, 0, G * dk, conv, 2 * G * dk, self.state[mx.key], o, m.q_start, m.q_len,
+        ops.lin_scan(ops.SCAN_DELTA, conv, 0, G * dk, conv, 2 * G * dk, self.state[self._key(mx)], o, m.q_start, m.q_len,
                      m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, G, dk, dv, z=z, zbias=mx.f["zbias"], hparam=mx.f["A_log"],
                      beta=proj, off_b=mx.off["b"], qscale=dk ** -0.5)
         return self._scan_out(mx, o, z, H * dk, 0, None, m, y)

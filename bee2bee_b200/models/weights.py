@@ -185,9 +185,45 @@ def lonulix_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, l
     return specs
 
 
+def fisopel_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
+    """(checkpoint name, shape, kind) of a Fisopel model; matrices are kept as [out, in].  The logits come from the
+    embedding table itself, so there is no head matrix; ``loop.in`` [width, 2 width] feeds every pass of the loop."""
+    W = cfg.hidden_size
+    specs = [("embed", (cfg.vocab_size, W), "w")] if (first or last) else []
+    if cfg.loop_in:
+        specs.append(("loop.in", (W, 2 * W), "w"))
+    for l in layers:
+        sp, p = cfg.layer_specs[l], f"l{l}."
+        m = p + "mix."
+        specs.append((p + "norm1", (W,), "one"))
+        if sp.mixer == "softmax_attention":
+            H, G, D, V = sp.heads, sp.kv_heads, sp.dim, sp.vdim
+            specs += [(m + "q", (H * D, W), "w"), (m + "k", (G * D, W), "w"), (m + "v", (G * V, W), "w"),
+                      (m + "q.norm", (D,), "one"), (m + "k.norm", (D,), "one"), (m + "sink", (H,), "bias"),
+                      (m + "o", (W, H * V), "w")]
+        elif sp.mixer == "latent_attention":
+            H, D, R, V, C = sp.heads, sp.dim, sp.rot_dim, sp.vdim, sp.kv_rank
+            specs += [(m + "q", (H * (D + R), W), "w"), (m + "dkv", (C + R, W), "w"), (m + "dkv.norm", (C,), "one"),
+                      (m + "uk", (H * D, C), "w"), (m + "uv", (H * V, C), "w"), (m + "g", (H * V, W), "w"),
+                      (m + "o", (W, H * V), "w")]
+        else:
+            raise ValueError(f"{cfg.name}: layer {l} has mixer {sp.mixer!r}, which is not part of this family")
+        if sp.ff:
+            specs.append((p + "norm2", (W,), "one"))
+            names = [f"e{e}" for e in range(sp.experts)] + (["shared"] if sp.shared_ff else [])
+            for n in names:
+                f = sp.shared_ff if n == "shared" else sp.expert_ff
+                specs += [(f"{p}mlp.{n}.gate", (f, W), "w"), (f"{p}mlp.{n}.up", (f, W), "w"), (f"{p}mlp.{n}.down", (W, f), "w")]
+            specs.append((p + "mlp.router", (sp.experts, W), "w"))
+    if last:
+        specs.append(("final.norm", (W,), "one"))
+    return specs
+
+
 def hybrid_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
     """tensor list of a hybrid family (configs with per-layer mixer specs)"""
-    fn = {"repudra": repudra_tensor_specs, "lonulix": lonulix_tensor_specs}.get(cfg.family, kepovik_tensor_specs)
+    fn = {"repudra": repudra_tensor_specs, "lonulix": lonulix_tensor_specs,
+          "fisopel": fisopel_tensor_specs}.get(cfg.family, kepovik_tensor_specs)
     return fn(cfg, layers, first, last)
 
 
@@ -196,7 +232,7 @@ def _init_random_hybrid(cfg: ModelConfig, layers, first, last, device, dtype, se
     for name, shape, kind in hybrid_tensor_specs(cfg, layers, first, last):
         if kind == "w":
             std = 1.0 if name in ("embed", "bigram") else shape[-1] ** -0.5
-            if cfg.family in ("repudra", "lonulix") and name == "embed":
+            if cfg.family in ("repudra", "lonulix", "fisopel") and name == "embed":
                 std = 1.0 / max(cfg.embed_scale, 1e-6)        # the scaled embedding has unit variance
             t[name] = _randn(name, shape, std, seed, device, dtype)
             continue

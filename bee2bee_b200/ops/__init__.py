@@ -35,7 +35,7 @@ _KERNEL_ENTRY_POINTS = ("add", "attention", "decode_advance", "embed", "fetch_wi
                         "set_decode_state", "hyb_embed", "hyb_commit_prev", "hc_step", "act_cols", "attn_prep",
                         "sig_attention", "delta_scan", "delta_post", "ls_join", "rot_attn_prep", "softmax_attention",
                         "short_conv", "mlstm_gates", "lin_scan", "scan_post", "post_norm_join", "latent_prep", "rot_heads",
-                        "moe_route", "gated_cols")
+                        "moe_route", "gated_cols", "head_up_gate")
 
 
 class _CountedModule:
@@ -529,17 +529,20 @@ def delta_post(o, gate, off_g, weight, out, T, H, dv, eps):
 
 # ------------------------------------------------------- parallel-block hybrids (one residual, layer scale, recurrences)
 def ls_join(x, q_start, q_len, n_seqs, max_q, *, terms=(), gamma=None, eps=1e-6, plus_one=False, h=None, rows=None,
-            n_rows=0):
+            n_rows=0, gamma2=None, h2=None, replace=False):
     """Residual join and next norm in one pass: ``x += sum_k w_k * y_k`` for up to three ``terms = (y, w, normed)``
     (``normed``: y is divided by its root mean square over the width first; ``w`` None = 1), then
     ``h = x / rms(x) * gamma`` (``gamma``: one gain or one per coordinate) as the GEMM operand.  ``rows`` gathers token
-    rows (logit rows) instead of walking the spans; the residual is then left as it is."""
+    rows (logit rows) instead of walking the spans; the residual is then left as it is.  ``replace``: the new residual
+    is the sum of the terms alone.  ``gamma`` None with ``h``: the operand is the residual itself.  ``gamma2`` / ``h2``: a
+    second normed operand of the same rows with its own weight vector (two sublayers side by side, a norm each)."""
     assert len(terms) <= 3
     t = list(terms) + [(None, None, False)] * (3 - len(terms))
     flat = []
     for y, w, normed in t:
         flat += [y, w, int(bool(normed))]
-    native().ls_join(x, q_start, q_len, rows, n_rows, n_seqs, max_q, *flat, eps, gamma, int(plus_one), h)
+    native().ls_join(x, q_start, q_len, rows, n_rows, n_seqs, max_q, *flat, eps, gamma, int(plus_one), h, gamma2, h2,
+                     int(bool(replace)))
 
 
 def rot_attn_prep(proj, off_q, off_k, off_v, qn, kn, freq, rdims, amp, positions, slots, q_out, k_cache, v_cache, T, H, G,
@@ -549,9 +552,11 @@ def rot_attn_prep(proj, off_q, off_k, off_v, qn, kn, freq, rdims, amp, positions
 
 
 def softmax_attention(q, k_cache, v_cache, out, block_table, q_start, q_len, kv_len, n_seqs, max_q, H, G, D, V, window,
-                      scale):
+                      scale, softcap=0.0, keep_first=0, sink=None):
+    """causal softmax attention over the paged cache; ``window`` > 0: the last ``window`` keys and the first ``keep_first``
+    ones; ``softcap`` > 0: ``score <- softcap * tanh(score / softcap)``; ``sink`` [H]: ``exp(sink_h)`` joins the denominator"""
     native().softmax_attention(q, k_cache, v_cache, out, block_table, q_start, q_len, kv_len, n_seqs, max_q, H, G, D, V,
-                               window, float(scale))
+                               window, float(scale), float(softcap), int(keep_first), sink)
 
 
 def short_conv(x, off, w, tail, y, q_start, q_len, kv_len, seq_slot, n_seqs, max_q):
@@ -591,23 +596,33 @@ def post_norm_join(x, *, w, h, y=None, gate=None, off_g=0, gbias=None, idw=None,
                             groups, float(eps), h)
 
 
-def latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, eps, T):
-    """latent attention: normed query latent -> ``cq``; cache row ``[rotated shared key part (R) | normed latent (C)]``"""
-    native().latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, float(eps), T)
+def latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, eps, T, amp=1.0):
+    """latent attention: normed query latent -> ``cq`` (``q_rank`` 0: there is none); cache row ``[rotated shared key part
+    (R) | normed latent (C)]``; ``amp`` multiplies cos and sin"""
+    native().latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, float(eps), T,
+                         float(amp))
 
 
-def rot_heads(src, off, dst, H, Dh, freq, rdims, positions, T, slots=None):
+def rot_heads(src, off, dst, H, Dh, freq, rdims, positions, T, slots=None, roff=0, amp=1.0):
     """``dst`` [T, H * Dh] (dense) = the ``H`` heads of ``Dh`` channels at column ``off`` of ``src`` with rotary positions
-    on the first ``rdims`` channels (pairs 2i, 2i+1) of each head"""
-    native().rot_heads(src, off, dst, H, Dh, freq, rdims, positions, slots, T)
+    on ``rdims`` channels (pairs 2i, 2i+1) of each head, from channel ``roff`` of the head on; ``amp`` multiplies cos and sin"""
+    native().rot_heads(src, off, dst, H, Dh, freq, rdims, positions, slots, T, int(roff), float(amp))
 
 
 def moe_route(proj, off, corr, n_real, count, keep, top, scale, wt, idw, T, sel_idx=None, sel_w=None):
     """softmax router over ``corr.numel()`` outputs (the last ones beyond ``n_real`` are identity experts): dense weight
-    rows ``wt`` [T, n_real] and the summed identity weight ``idw`` [T]; optionally the choices in order"""
-    native().moe_route(proj, off, corr, n_real, count, keep, top, float(scale), wt, idw, sel_idx, sel_w, T)
+    rows ``wt`` [T, n_real] and the summed identity weight ``idw`` [T]; optionally the choices in order.  ``corr`` None:
+    ``n_real`` outputs, the largest logits are chosen and the weights are the softmax over the chosen logits alone"""
+    native().moe_route(proj, off, corr, corr.numel() if corr is not None else n_real, n_real, count, keep, top,
+                       float(scale), wt, idw, sel_idx, sel_w, T)
 
 
-def gated_cols(x, off_a, off_b, out, n, act, T, wt=None, per=0):
-    """``out[t, c] = act(x[t, off_a + c]) * x[t, off_b + c]``, or ``* wt[t, c // per]`` with per-expert weights"""
-    native().gated_cols(x, off_a, off_b, wt, per, out, n, act, T)
+def gated_cols(x, off_a, off_b, out, n, act, T, wt=None, per=0, both=False, lead=0):
+    """``out[t, c] = act(x[t, off_a + c]) * x[t, off_b + c]``, or ``* wt[t, c // per]`` with per-expert weights, or
+    (``both``) times the two of them, the first ``lead`` columns having weight 1 (a shared expert in front of the routed ones)"""
+    native().gated_cols(x, off_a, off_b, wt, per, out, n, act, T, int(bool(both)), int(lead))
+
+
+def head_up_gate(a, U, out, T, H, V, C, gate=None, off_g=0):
+    """``out[t, h V + v] = sigmoid(gate[t, off_g + h V + v]) * sum_c U[h, v, c] a[t, h C + c]`` (no gate: the plain product)"""
+    native().head_up_gate(a, U, gate, off_g, out, T, H, V, C)

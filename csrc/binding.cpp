@@ -539,10 +539,15 @@ void delta_post(const Tensor& o, const Tensor& gate, int64_t off_g, const Tensor
 void ls_join(const Tensor& x, const Tensor& q_start, const Tensor& q_len, const OptT& rows, int64_t n_rows, int64_t n_seqs,
              int64_t max_q, const OptT& y0, const OptT& w0, int64_t norm0, const OptT& y1, const OptT& w1, int64_t norm1,
              const OptT& y2, const OptT& w2, int64_t norm2, double eps, const OptT& gamma, int64_t plus_one,
-             const OptT& h) {
+             const OptT& h, const OptT& gamma2, const OptT& h2, int64_t replace) {
   c10::cuda::CUDAGuard guard(x.device());
   const bool has_h = h.has_value() && h->defined();
-  TORCH_CHECK(has_h == (gamma.has_value() && gamma->defined()), "ls_join: h and gamma come together");
+  const bool has_g = gamma.has_value() && gamma->defined();
+  const bool has_h2 = h2.has_value() && h2->defined();
+  TORCH_CHECK(has_h || !has_g, "ls_join: a norm weight needs an operand to write");
+  TORCH_CHECK(!has_h2 || (has_h && has_g && gamma2.has_value() && gamma2->defined() && gamma2->numel() == x.size(-1) &&
+                          h2->scalar_type() == h->scalar_type()),
+              "ls_join: the second operand needs the first one and a weight vector of its own");
   auto ld = [](const OptT& t) { return (t.has_value() && t->defined()) ? static_cast<int>(t->stride(0)) : 0; };
   const int W = static_cast<int>(x.size(-1));
   check(b2b::launch_ls_join(const_cast<float*>(fp(x)), ip(q_start), ip(q_len),
@@ -550,9 +555,10 @@ void ls_join(const Tensor& x, const Tensor& q_start, const Tensor& q_len, const 
                             static_cast<int>(n_seqs), static_cast<int>(max_q), fp_or_null(y0), ld(y0), fp_or_null(w0),
                             static_cast<int>(norm0), fp_or_null(y1), ld(y1), fp_or_null(w1), static_cast<int>(norm1),
                             fp_or_null(y2), ld(y2), fp_or_null(w2), static_cast<int>(norm2), static_cast<float>(eps),
-                            fp_or_null(gamma), (has_h && gamma->numel() > 1) ? 1 : 0, static_cast<int>(plus_one),
+                            fp_or_null(gamma), (has_g && gamma->numel() > 1) ? 1 : 0, static_cast<int>(plus_one),
                             has_h ? h->data_ptr() : nullptr, has_h ? static_cast<int>(h->stride(0)) : 0, W,
-                            has_h ? is_f32(*h) : 1, cur_stream()),
+                            has_h ? is_f32(*h) : 1, has_h2 ? fp(*gamma2) : nullptr, has_h2 ? h2->data_ptr() : nullptr,
+                            has_h2 ? static_cast<int>(h2->stride(0)) : 0, static_cast<int>(replace), cur_stream()),
         "ls_join");
 }
 
@@ -575,8 +581,9 @@ void rot_attn_prep(const Tensor& proj, int64_t off_q, int64_t off_k, int64_t off
 void softmax_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& out,
                        const Tensor& block_table, const Tensor& q_start, const Tensor& q_len, const Tensor& kv_len,
                        int64_t n_seqs, int64_t max_q, int64_t H, int64_t G, int64_t D, int64_t V, int64_t window,
-                       double scale) {
+                       double scale, double softcap, int64_t keep_first, const OptT& sink) {
   c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(!(sink.has_value() && sink->defined()) || sink->numel() >= H, "softmax_attention: one sink per head");
   TORCH_CHECK(k_cache.scalar_type() == out.scalar_type() && v_cache.scalar_type() == out.scalar_type(),
               "softmax_attention: cache and output dtypes must match");
   check(b2b::launch_softmax_attention(fp(q), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
@@ -585,7 +592,8 @@ void softmax_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                                       static_cast<int>(n_seqs), static_cast<int>(max_q), static_cast<int>(H),
                                       static_cast<int>(G), static_cast<int>(D), static_cast<int>(V),
                                       static_cast<int>(window), static_cast<float>(scale),
-                                      static_cast<int>(v_cache.stride(1)), is_f32(out), cur_stream()),
+                                      static_cast<int>(v_cache.stride(1)), is_f32(out), static_cast<float>(softcap),
+                                      static_cast<int>(keep_first), fp_or_null(sink), cur_stream()),
         "softmax_attention");
 }
 
@@ -666,7 +674,7 @@ void post_norm_join(const Tensor& x, const OptT& rows, int64_t n_rows, const Opt
 
 void latent_prep(const Tensor& proj, int64_t off_q, int64_t q_rank, int64_t off_kv, int64_t C, int64_t R, const Tensor& wq,
                  const Tensor& wc, const Tensor& freq, int64_t rdims, const Tensor& positions, const Tensor& slots,
-                 const Tensor& cq, const Tensor& k_cache, double eps, int64_t T) {
+                 const Tensor& cq, const Tensor& k_cache, double eps, int64_t T, double amp) {
   c10::cuda::CUDAGuard guard(proj.device());
   TORCH_CHECK(cq.scalar_type() == k_cache.scalar_type(), "latent_prep: operand and cache dtypes must match");
   TORCH_CHECK(k_cache.size(-1) == R + C && k_cache.is_contiguous(), "latent_prep: cache rows are [rotary | latent]");
@@ -675,29 +683,31 @@ void latent_prep(const Tensor& proj, int64_t off_q, int64_t q_rank, int64_t off_
                                 static_cast<int>(q_rank), static_cast<int>(off_kv), static_cast<int>(C),
                                 static_cast<int>(R), fp(wq), fp(wc), fp(freq), static_cast<int>(rdims), ip(positions),
                                 ip(slots), cq.data_ptr(), static_cast<int>(cq.stride(0)), k_cache.data_ptr(),
-                                static_cast<float>(eps), static_cast<int>(T), is_f32(cq), cur_stream()),
+                                static_cast<float>(eps), static_cast<int>(T), is_f32(cq), static_cast<float>(amp),
+                                cur_stream()),
         "latent_prep");
 }
 
 void rot_heads(const Tensor& src, int64_t off, const Tensor& dst, int64_t H, int64_t Dh, const Tensor& freq, int64_t rdims,
-               const Tensor& positions, const OptT& slots, int64_t T) {
+               const Tensor& positions, const OptT& slots, int64_t T, int64_t roff, double amp) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(rdims == 0 || freq.numel() >= rdims / 2, "rot_heads: frequency table too short");
   TORCH_CHECK(dst.is_contiguous() && dst.size(-1) == H * Dh, "rot_heads: dense [T, H * Dh] output");
   check(b2b::launch_rot_heads(fp(src), static_cast<int>(src.stride(0)), static_cast<int>(off), const_cast<float*>(fp(dst)),
                               static_cast<int>(H), static_cast<int>(Dh), fp(freq), static_cast<int>(rdims), ip(positions),
                               (slots.has_value() && slots->defined()) ? ip(*slots) : nullptr, static_cast<int>(T),
-                              cur_stream()),
+                              static_cast<int>(roff), static_cast<float>(amp), cur_stream()),
         "rot_heads");
 }
 
-void moe_route(const Tensor& proj, int64_t off, const Tensor& corr, int64_t n_real, int64_t count, int64_t keep,
+void moe_route(const Tensor& proj, int64_t off, const OptT& corr, int64_t E, int64_t n_real, int64_t count, int64_t keep,
                int64_t top, double scale, const Tensor& wt, const Tensor& idw, const OptT& sel_idx, const OptT& sel_w,
                int64_t T) {
   c10::cuda::CUDAGuard guard(proj.device());
   const bool has_sel = sel_idx.has_value() && sel_idx->defined();
-  check(b2b::launch_moe_route(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off), fp(corr),
-                              static_cast<int>(corr.numel()), static_cast<int>(n_real), static_cast<int>(count),
+  TORCH_CHECK(!(corr.has_value() && corr->defined()) || corr->numel() == E, "moe_route: one correction per router output");
+  check(b2b::launch_moe_route(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off), fp_or_null(corr),
+                              static_cast<int>(E), static_cast<int>(n_real), static_cast<int>(count),
                               static_cast<int>(keep), static_cast<int>(top), static_cast<float>(scale),
                               const_cast<float*>(fp(wt)), static_cast<int>(wt.stride(0)), const_cast<float*>(fp(idw)),
                               has_sel ? const_cast<int*>(ip(*sel_idx)) : nullptr,
@@ -706,14 +716,30 @@ void moe_route(const Tensor& proj, int64_t off, const Tensor& corr, int64_t n_re
 }
 
 void gated_cols(const Tensor& in, int64_t off_a, int64_t off_b, const OptT& wt, int64_t per, const Tensor& out, int64_t n,
-                int64_t act, int64_t T) {
+                int64_t act, int64_t T, int64_t both, int64_t lead) {
   c10::cuda::CUDAGuard guard(in.device());
   const bool has_wt = wt.has_value() && wt->defined();
   check(b2b::launch_gated_cols(fp(in), static_cast<int>(in.stride(0)), static_cast<int>(off_a), static_cast<int>(off_b),
                                fp_or_null(wt), has_wt ? static_cast<int>(wt->stride(0)) : 0,
                                static_cast<int>(per > 0 ? per : 1), out.data_ptr(), static_cast<int>(out.stride(0)),
-                               static_cast<int>(n), static_cast<int>(act), static_cast<int>(T), is_f32(out), cur_stream()),
+                               static_cast<int>(n), static_cast<int>(act), static_cast<int>(T), is_f32(out),
+                               static_cast<int>(both), static_cast<int>(lead), cur_stream()),
         "gated_cols");
+}
+
+// a [T, >= H * C] per-head latent rows, U [H, V, C]; out [T, >= H * V] = sigmoid(gate[:, off_g + h V + v]) * (U[h] a[t, h])
+void head_up_gate(const Tensor& a, const Tensor& U, const OptT& gate, int64_t off_g, const Tensor& out, int64_t T, int64_t H,
+                  int64_t V, int64_t C) {
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.scalar_type() == U.scalar_type() && a.scalar_type() == out.scalar_type(), "head_up_gate: operand dtypes must match");
+  TORCH_CHECK(U.is_contiguous() && U.numel() == H * V * C, "head_up_gate: U is a dense [H, V, C]");
+  TORCH_CHECK(a.size(-1) >= H * C && out.size(-1) >= H * V, "head_up_gate: rows too short");
+  const bool has_g = gate.has_value() && gate->defined();
+  check(b2b::launch_head_up_gate(a.data_ptr(), static_cast<int>(a.stride(0)), U.data_ptr(), fp_or_null(gate),
+                                 has_g ? static_cast<int>(gate->stride(0)) : 0, static_cast<int>(off_g), out.data_ptr(),
+                                 static_cast<int>(out.stride(0)), static_cast<int>(T), static_cast<int>(H),
+                                 static_cast<int>(V), static_cast<int>(C), is_f32(out), cur_stream()),
+        "head_up_gate");
 }
 }  // namespace
 
@@ -774,4 +800,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rot_heads", &rot_heads);
   m.def("moe_route", &moe_route);
   m.def("gated_cols", &gated_cols);
+  m.def("head_up_gate", &head_up_gate);
 }

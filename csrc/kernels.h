@@ -94,7 +94,8 @@ int launch_delta_post(const float* o, int ld_o, const float* gate, int ld_g, int
 int launch_ls_join(float* x, const int* q_start, const int* q_len, const int* rows, int n_rows, int n_seqs, int max_q,
                    const float* y0, int ld0, const float* w0, int norm0, const float* y1, int ld1, const float* w1,
                    int norm1, const float* y2, int ld2, const float* w2, int norm2, float eps, const float* gamma,
-                   int gstride, int plus_one, void* h, int ld_h, int W, int f32, cudaStream_t s);
+                   int gstride, int plus_one, void* h, int ld_h, int W, int f32, const float* gamma2, void* h2, int ld_h2,
+                   int replace, cudaStream_t s);
 int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int off_v, const float* qn, const float* kn,
                          const float* freq, int rdims, float amp, const int* positions, const int* slots, float* q_out,
                          void* k_cache, void* v_cache, int T, int H, int G, int D, int V, float eps, int f32,
@@ -102,7 +103,8 @@ int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int of
 int launch_softmax_attention(const float* q, const void* k_cache, const void* v_cache, void* out, int ld_out,
                              const int* block_table, int max_pages, const int* q_start, const int* q_len,
                              const int* kv_len, int n_seqs, int max_q, int H, int G, int D, int V, int window,
-                             float scale, int ldv, int f32, cudaStream_t s);
+                             float scale, int ldv, int f32, float softcap, int keep_first, const float* sink,
+                             cudaStream_t s);
 int launch_short_conv(const float* x, int ld_x, int off, const float* w, float* tail, float* y, int ld_y,
                       const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs,
                       int max_q, int C, int taps, cudaStream_t s);
@@ -131,14 +133,17 @@ int launch_post_norm_join(float* x, const int* rows, int n_rows, const float* y,
                           float eps, void* h, int ld_h, int W, int f32, cudaStream_t s);
 int launch_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int C, int R, const float* wq,
                        const float* wc, const float* freq, int rdims, const int* positions, const int* slots, void* cq,
-                       int ld_cq, void* k_cache, float eps, int T, int f32, cudaStream_t s);
+                       int ld_cq, void* k_cache, float eps, int T, int f32, float amp, cudaStream_t s);
 int launch_rot_heads(const float* src, int ld, int off, float* dst, int H, int Dh, const float* freq, int rdims,
-                     const int* positions, const int* slots, int T, cudaStream_t s);
+                     const int* positions, const int* slots, int T, int roff, float amp, cudaStream_t s);
 int launch_moe_route(const float* proj, int ld, int off, const float* corr, int E, int n_real, int count, int keep,
                      int top, float scale, float* wt, int ld_wt, float* idw, int* sel_idx, float* sel_w, int T,
                      cudaStream_t s);
 int launch_gated_cols(const float* in, int ld_in, int off_a, int off_b, const float* wt, int ld_wt, int per, void* out,
-                      int ld_out, int n, int act, int T, int f32, cudaStream_t s);
+                      int ld_out, int n, int act, int T, int f32, int both, int lead, cudaStream_t s);
+// out[t, h, :] = gate * U[h] a[t, h, :]: one [V, C] matrix per head (operands bf16, or float when f32), sigmoid gate from fp32 rows
+int launch_head_up_gate(const void* a, int ld_a, const void* U, const float* gate, int ld_g, int off_g, void* out,
+                        int ld_out, int T, int H, int V, int C, int f32, cudaStream_t s);
 
 // bounded handoff waits: device abort word + time limit for the waits of each translation unit (0 / null = trap policy)
 int set_wait_policy_gemm(uint32_t* abort_word, unsigned long long limit_ns);

@@ -9,7 +9,8 @@
 //   * rot_heads        rotary positions on the first channels of every head of a projection -> dense query rows
 //   * moe_route        softmax router with a selection-only correction, group-limited top-k and identity experts
 //   * gated_cols       out = act(a) * b for two column blocks, or act(a) * per-expert weight (routed experts run as one
-//                      stacked up-projection whose hidden columns are scaled by the token's weight for their expert)
+//                      stacked up-projection whose hidden columns are scaled by the token's weight for their expert), or both
+//   * head_up_gate     a [V, C] matrix per head applied to per-head latent rows, times a sigmoid output gate
 // Norms, gates, router, angles and the residual are fp32 in every mode; OT / CT (operand / cache type) is bf16 or float.
 // This translation unit is compiled WITHOUT --use_fast_math (exact expf / erff / division / sqrt / sincos).
 #include "kernels.h"
@@ -30,6 +31,8 @@ template <> __device__ __forceinline__ void stf<float>(float* p, size_t i, float
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ float sigmoid_(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float ldf_(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float ldf_(const bf16* p, size_t i) { return __bfloat162float(p[i]); }
 
 __device__ __forceinline__ void pdl_begin() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -184,14 +187,14 @@ __global__ void __launch_bounds__(256)
 // the rotary key part (R columns) that all heads share.  One warp per token:
 //   cq[t]            = rms(query latent) * wq                      (operand of the query up-projection)
 //   k_cache[slot]    = [ rotate(rotary part) | rms(latent) * wc ]  (the only thing a token leaves in the cache)
-// Rotation: channels (2i, 2i+1), 2i < rdims, turn by positions[t] * freq[i].
+// Rotation: channels (2i, 2i+1), 2i < rdims, turn by positions[t] * freq[i]; cos and sin are multiplied by amp.
 constexpr int LAT_WARPS = 4;                  // one warp per token: a token's latents are a few hundred channels
 template <typename OT, typename CT>
 __global__ void __launch_bounds__(32 * LAT_WARPS)
     latent_prep_kernel(const float* __restrict__ proj, int ld, int off_q, int q_rank, int off_kv, int C, int R,
                        const float* __restrict__ wq, const float* __restrict__ wc, const float* __restrict__ freq,
                        int rdims, const int* __restrict__ positions, const int* __restrict__ slots, OT* __restrict__ cq,
-                       int ld_cq, CT* __restrict__ k_cache, float eps, int T) {
+                       int ld_cq, CT* __restrict__ k_cache, float eps, int T, float amp) {
   pdl_begin();
   const int t = blockIdx.x * LAT_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -203,7 +206,7 @@ __global__ void __launch_bounds__(32 * LAT_WARPS)
   float sq = 0.f, sc = 0.f;
   for (int i = lane; i < q_rank; i += 32) sq += ql[i] * ql[i];
   for (int i = lane; i < C; i += 32) sc += cl[i] * cl[i];
-  const float rq = 1.f / sqrtf(warp_sum_(sq) / static_cast<float>(q_rank) + eps);
+  const float rq = 1.f / sqrtf(warp_sum_(sq) / static_cast<float>(max(q_rank, 1)) + eps);     // q_rank = 0: no query latent
   const float rc = 1.f / sqrtf(warp_sum_(sc) / static_cast<float>(C) + eps);
   for (int i = lane; i < q_rank; i += 32) stf(cq, static_cast<size_t>(t) * ld_cq + i, ql[i] * rq * wq[i]);
   CT* krow = k_cache + static_cast<size_t>(slot) * (R + C);
@@ -213,6 +216,8 @@ __global__ void __launch_bounds__(32 * LAT_WARPS)
   for (int i = lane; i < rdims / 2; i += 32) {        // a lane turns whole pairs
     float sn, cs;
     sincosf(pos * freq[i], &sn, &cs);
+    sn *= amp;
+    cs *= amp;
     const float u = kr[2 * i], v = kr[2 * i + 1];
     stf(krow, 2 * i, u * cs - v * sn);
     stf(krow, 2 * i + 1, v * cs + u * sn);
@@ -220,25 +225,25 @@ __global__ void __launch_bounds__(32 * LAT_WARPS)
   for (int i = rdims + lane; i < R; i += 32) stf(krow, i, kr[i]);
 }
 
-// src [T, ld] fp32 holds H heads of Dh channels at column off; dst [T, H * Dh] (dense) receives them with the first
-// rdims channels of every head turned by positions[t] * freq[pair] (pairs 2i, 2i+1).
+// src [T, ld] fp32 holds H heads of Dh channels at column off; dst [T, H * Dh] (dense) receives them with the rdims
+// channels from channel roff of every head on turned by positions[t] * freq[pair] (pairs 2i, 2i+1) and multiplied by amp.
 __global__ void rot_heads_kernel(const float* __restrict__ src, int ld, int off, float* __restrict__ dst, int H, int Dh,
                                  const float* __restrict__ freq, int rdims, const int* __restrict__ positions,
-                                 const int* __restrict__ slots, int T) {
+                                 const int* __restrict__ slots, int T, int roff, float amp) {
   pdl_begin();
   const int n = H * Dh;
   const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (e >= static_cast<long long>(T) * n) return;
   const int c = static_cast<int>(e % n), t = static_cast<int>(e / n);
   if (slots != nullptr && slots[t] < 0) return;
-  const int d = c % Dh;
+  const int d = c % Dh - roff;                        // channel within the rotated part of its head
   const float* row = src + static_cast<size_t>(t) * ld + off;
   float v = row[c];
-  if (d < rdims) {
+  if (d >= 0 && d < rdims) {
     float sn, cs;
     sincosf(static_cast<float>(positions[t]) * freq[d >> 1], &sn, &cs);
     const float o = row[c - d + (d ^ 1)];             // the other channel of the pair (2i, 2i+1) of this head
-    v = (d & 1) ? v * cs + o * sn : v * cs - o * sn;
+    v = ((d & 1) ? v * cs + o * sn : v * cs - o * sn) * amp;
   }
   dst[static_cast<size_t>(t) * n + c] = v;
 }
@@ -247,7 +252,8 @@ __global__ void rot_heads_kernel(const float* __restrict__ src, int ld, int off,
 // One warp per token.  z = logits [E] (fp32, column off of proj), s = softmax(z); choice = s + corr; consecutive experts
 // are bundled into `count` equal groups, a group's score is its largest choice, only experts of the `keep` best groups stay
 // candidates; the `top` candidates with the largest choice are chosen (ties: the lower index); their weights are
-// s / (sum of the chosen s + 1e-20) * scale.  Experts n_real .. E - 1 are identity experts: their weights are summed into
+// s / (sum of the chosen s + 1e-20) * scale (= the softmax over the chosen logits alone when scale = 1).  corr == nullptr:
+// the choice is made on the logits themselves.  Experts n_real .. E - 1 are identity experts: their weights are summed into
 // idw[t]; wt [T, ld_wt] receives the dense weight row of the real experts (0 = not chosen).  sel_idx / sel_w [T, top]
 // (optional) list the choices in order.
 __global__ void __launch_bounds__(128)
@@ -278,7 +284,7 @@ __global__ void __launch_bounds__(128)
   for (int j = lane; j < E; j += 32) {
     const float p = s[j] / den;
     s[j] = p;
-    ch[j] = p + corr[j];
+    ch[j] = corr != nullptr ? p + corr[j] : z[j];      // no correction: the largest logits themselves are chosen
   }
   __syncwarp();
   // warp arg-max over an array of n floats (lowest index among equals)
@@ -352,7 +358,9 @@ __global__ void __launch_bounds__(128)
 }
 
 // ------------------------------------------------------------------------------------------- gated columns
-// out[t, c] = act(in[t, off_a + c]) * (wt == nullptr ? in[t, off_b + c] : wt[t, c / per]) for c < n.
+// out[t, c] = act(in[t, off_a + c]) * (wt == nullptr ? in[t, off_b + c] : wt[t, c / per]) for c < n.  both != 0 (with wt):
+// act(a) * in[t, off_b + c] * weight, where the first `lead` columns have weight 1 and column c >= lead has
+// wt[t, (c - lead) / per] (gated experts side by side behind a shared one).
 // act: 0 silu, 1 exact (erf) gelu, 2 tanh gelu.  Four columns per thread when every offset allows 16-byte accesses.
 __device__ __forceinline__ float act_(float z, int act) {
   if (act == 0) return z / (1.f + expf(-z));
@@ -362,14 +370,15 @@ __device__ __forceinline__ float act_(float z, int act) {
 template <typename OT>
 __global__ void __launch_bounds__(256)
     gated_cols_kernel(const float* __restrict__ in, int ld_in, int off_a, int off_b, const float* __restrict__ wt,
-                      int ld_wt, int per, OT* __restrict__ out, int ld_out, int n, int act, int T) {
+                      int ld_wt, int per, OT* __restrict__ out, int ld_out, int n, int act, int T, int both, int lead) {
   pdl_begin();
   const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (e >= static_cast<long long>(T) * n) return;
   const int c = static_cast<int>(e % n);
   const size_t t = static_cast<size_t>(e / n);
   const float a = act_(in[t * ld_in + off_a + c], act);
-  const float b = wt != nullptr ? wt[t * ld_wt + c / per] : in[t * ld_in + off_b + c];
+  float b = wt != nullptr ? (c < lead ? 1.f : wt[t * ld_wt + (c - lead) / per]) : in[t * ld_in + off_b + c];
+  if (both && wt != nullptr) b *= in[t * ld_in + off_b + c];
   stf(out, t * ld_out + c, a * b);
 }
 
@@ -377,7 +386,7 @@ __global__ void __launch_bounds__(256)
 template <typename OT>
 __global__ void __launch_bounds__(256)
     gated_cols_vec_kernel(const float* __restrict__ in, int ld_in, int off_a, int off_b, const float* __restrict__ wt,
-                          int ld_wt, int per, OT* __restrict__ out, int ld_out, int n, int act) {
+                          int ld_wt, int per, OT* __restrict__ out, int ld_out, int n, int act, int both, int lead) {
   pdl_begin();
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= n) return;
@@ -385,17 +394,99 @@ __global__ void __launch_bounds__(256)
   const float4 a = *reinterpret_cast<const float4*>(in + t * ld_in + off_a + c);
   float4 b;
   if (wt != nullptr) {
-    const float wv = wt[t * ld_wt + c / per];          // per is a multiple of four: one expert for the four columns
+    const float wv = c < lead ? 1.f : wt[t * ld_wt + (c - lead) / per];      // per and lead are multiples of four: one expert for the four columns
     b = make_float4(wv, wv, wv, wv);
+    if (both) {
+      const float4 u = *reinterpret_cast<const float4*>(in + t * ld_in + off_b + c);
+      b = make_float4(wv * u.x, wv * u.y, wv * u.z, wv * u.w);
+    }
   } else {
     b = *reinterpret_cast<const float4*>(in + t * ld_in + off_b + c);
   }
   st4(out + t * ld_out + c, make_float4(act_(a.x, act) * b.x, act_(a.y, act) * b.y, act_(a.z, act) * b.z, act_(a.w, act) * b.w));
 }
 
+// ------------------------------------------------------------------------------------------- per-head up-projection
+// out[t, h * V + v] = gate(t, h * V + v) * sum_c a[t, h * C + c] * U[h, v, c]: every head has its own [V, C] matrix (the
+// value up-projection of latent attention, applied to the attention output taken over the latents), so this is a batch
+// of H small matrix products.  gate (optional) = sigmoid of column off_g + h * V + v of an fp32 row (the output gate of the
+// concatenated heads).  A block = 64 tokens x 64 value channels of one head, 256 threads with 4 x 4 outputs each, the
+// latent dimension walked in slices of 16 through shared memory; fp32 accumulation.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+    head_up_gate_kernel(const OT* __restrict__ a, int ld_a, const OT* __restrict__ U, const float* __restrict__ gate,
+                        int ld_g, int off_g, OT* __restrict__ out, int ld_out, int T, int H, int V, int C) {
+  pdl_begin();
+  __shared__ float As[16][64 + 4];       // [c][token]
+  __shared__ float Us[16][64 + 4];       // [c][value channel]
+  const int h = blockIdx.z, t0 = blockIdx.x * 64, v0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // tx: value channels, ty: tokens
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const OT* ah = a + static_cast<size_t>(h) * C;
+  const OT* uh = U + static_cast<size_t>(h) * V * C;
+  for (int c0 = 0; c0 < C; c0 += 16) {
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+      const int r = e >> 4, c = e & 15;                          // consecutive threads walk the latent channels of a row
+      const int t = t0 + r, v = v0 + r;
+      float av = 0.f, uv = 0.f;
+      if (c0 + c < C) {
+        if (t < T) av = ldf_(ah + static_cast<size_t>(t) * ld_a, c0 + c);
+        if (v < V) uv = ldf_(uh + static_cast<size_t>(v) * C, c0 + c);
+      }
+      As[c][r] = av;
+      Us[c][r] = uv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      float av[4], uv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[c][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) uv[j] = Us[c][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * uv[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + ty * 4 + i;
+    if (t >= T) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int v = v0 + tx * 4 + j;
+      if (v >= V) continue;
+      float o = acc[i][j];
+      if (gate != nullptr) o *= sigmoid_(gate[static_cast<size_t>(t) * ld_g + off_g + h * V + v]);
+      stf(out, static_cast<size_t>(t) * ld_out + h * V + v, o);
+    }
+  }
+}
+
 inline int last_error() { return static_cast<int>(cudaGetLastError()); }
 
 }  // namespace
+
+int launch_head_up_gate(const void* a, int ld_a, const void* U, const float* gate, int ld_g, int off_g, void* out,
+                        int ld_out, int T, int H, int V, int C, int f32, cudaStream_t s) {
+  if (T <= 0 || H <= 0 || V <= 0) return 0;
+  if (C <= 0 || H > 65535) return -2;
+  const dim3 grid((T + 63) / 64, (V + 63) / 64, H);
+  if (f32)
+    launch_kernel(head_up_gate_kernel<float>, grid, dim3(256), 0, s, 1u, static_cast<const float*>(a), ld_a,
+                  static_cast<const float*>(U), gate, ld_g, off_g, static_cast<float*>(out), ld_out, T, H, V, C);
+  else
+    launch_kernel(head_up_gate_kernel<bf16>, grid, dim3(256), 0, s, 1u, static_cast<const bf16*>(a), ld_a,
+                  static_cast<const bf16*>(U), gate, ld_g, off_g, static_cast<bf16*>(out), ld_out, T, H, V, C);
+  return last_error();
+}
 
 int launch_post_norm_join(float* x, const int* rows, int n_rows, const float* y, int ld_y, const float* gate, int ld_g,
                           int off_g, const float* gbias, const float* idw, float alpha, const float* w, int groups,
@@ -445,26 +536,26 @@ int launch_post_norm_join(float* x, const int* rows, int n_rows, const float* y,
 
 int launch_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int C, int R, const float* wq,
                        const float* wc, const float* freq, int rdims, const int* positions, const int* slots, void* cq,
-                       int ld_cq, void* k_cache, float eps, int T, int f32, cudaStream_t s) {
+                       int ld_cq, void* k_cache, float eps, int T, int f32, float amp, cudaStream_t s) {
   if (T <= 0) return 0;
   if (rdims < 0 || rdims > R || rdims % 2 != 0) return -2;
   const dim3 grid((T + LAT_WARPS - 1) / LAT_WARPS), block(32 * LAT_WARPS);
   if (f32)
     launch_kernel(latent_prep_kernel<float, float>, grid, block, 0, s, 1u, proj, ld, off_q, q_rank, off_kv, C, R, wq, wc,
-                  freq, rdims, positions, slots, static_cast<float*>(cq), ld_cq, static_cast<float*>(k_cache), eps, T);
+                  freq, rdims, positions, slots, static_cast<float*>(cq), ld_cq, static_cast<float*>(k_cache), eps, T, amp);
   else
     launch_kernel(latent_prep_kernel<bf16, bf16>, grid, block, 0, s, 1u, proj, ld, off_q, q_rank, off_kv, C, R, wq, wc,
-                  freq, rdims, positions, slots, static_cast<bf16*>(cq), ld_cq, static_cast<bf16*>(k_cache), eps, T);
+                  freq, rdims, positions, slots, static_cast<bf16*>(cq), ld_cq, static_cast<bf16*>(k_cache), eps, T, amp);
   return last_error();
 }
 
 int launch_rot_heads(const float* src, int ld, int off, float* dst, int H, int Dh, const float* freq, int rdims,
-                     const int* positions, const int* slots, int T, cudaStream_t s) {
+                     const int* positions, const int* slots, int T, int roff, float amp, cudaStream_t s) {
   const long long n = static_cast<long long>(T) * H * Dh;
   if (n <= 0) return 0;
-  if (rdims > Dh || rdims % 2 != 0) return -2;
+  if (roff < 0 || roff + rdims > Dh || rdims % 2 != 0) return -2;
   launch_kernel(rot_heads_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, 1u, src, ld, off, dst, H, Dh,
-                freq, rdims, positions, slots, T);
+                freq, rdims, positions, slots, T, roff, amp);
   return last_error();
 }
 
@@ -473,6 +564,7 @@ int launch_moe_route(const float* proj, int ld, int off, const float* corr, int 
                      cudaStream_t s) {
   if (T <= 0) return 0;
   if (E <= 0 || n_real < 0 || n_real > E || count <= 0 || E % count != 0 || top <= 0 || top > E) return -2;
+  if (corr == nullptr && count > 1 && keep < count) return -2;      // group-limited choice is defined on corrected scores
   int warps = 4;
   while (warps > 1 && static_cast<size_t>(warps) * 4 * E * sizeof(float) > 40 * 1024) warps /= 2;
   const size_t smem = static_cast<size_t>(warps) * 4 * E * sizeof(float);
@@ -483,27 +575,28 @@ int launch_moe_route(const float* proj, int ld, int off, const float* corr, int 
 }
 
 int launch_gated_cols(const float* in, int ld_in, int off_a, int off_b, const float* wt, int ld_wt, int per, void* out,
-                      int ld_out, int n, int act, int T, int f32, cudaStream_t s) {
+                      int ld_out, int n, int act, int T, int f32, int both, int lead, cudaStream_t s) {
   const long long tot = static_cast<long long>(T) * n;
   if (tot <= 0) return 0;
-  if (n % 4 == 0 && ld_in % 4 == 0 && off_a % 4 == 0 && (wt != nullptr ? per % 4 == 0 : off_b % 4 == 0) &&
+  if (n % 4 == 0 && ld_in % 4 == 0 && off_a % 4 == 0 && (wt != nullptr ? per % 4 == 0 && lead % 4 == 0 : off_b % 4 == 0) &&
+      (!both || off_b % 4 == 0) &&
       ld_out % 4 == 0 && T <= 65535 && reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
     const dim3 vgrid((n / 4 + 255) / 256, T);
     if (f32)
       launch_kernel(gated_cols_vec_kernel<float>, vgrid, dim3(256), 0, s, 1u, in, ld_in, off_a, off_b, wt, ld_wt, per,
-                    static_cast<float*>(out), ld_out, n, act);
+                    static_cast<float*>(out), ld_out, n, act, both, lead);
     else
       launch_kernel(gated_cols_vec_kernel<bf16>, vgrid, dim3(256), 0, s, 1u, in, ld_in, off_a, off_b, wt, ld_wt, per,
-                    static_cast<bf16*>(out), ld_out, n, act);
+                    static_cast<bf16*>(out), ld_out, n, act, both, lead);
     return last_error();
   }
   const dim3 grid(static_cast<unsigned>((tot + 255) / 256));
   if (f32)
     launch_kernel(gated_cols_kernel<float>, grid, dim3(256), 0, s, 1u, in, ld_in, off_a, off_b, wt, ld_wt, per,
-                  static_cast<float*>(out), ld_out, n, act, T);
+                  static_cast<float*>(out), ld_out, n, act, T, both, lead);
   else
     launch_kernel(gated_cols_kernel<bf16>, grid, dim3(256), 0, s, 1u, in, ld_in, off_a, off_b, wt, ld_wt, per,
-                  static_cast<bf16*>(out), ld_out, n, act, T);
+                  static_cast<bf16*>(out), ld_out, n, act, T, both, lead);
   return last_error();
 }
 

@@ -82,6 +82,8 @@ struct JoinTerm {
 // when plus_one.  WPT warps per token (1: narrow models, no block barrier; LSJ_WARPS: the block is one token): pass 1
 // sums the squares of the terms that are normed, pass 2 builds the new residual row (kept in shared memory) and its sum
 // of squares, pass 3 writes the operand.  VEC: 16-byte accesses (W and every row stride multiples of 4).
+// replace: the new residual row is the sum of the terms alone (the old row is not read).  gamma == nullptr: the operand is
+// the residual row itself.  gamma2 / h2: a second normed operand of the same row (blocks whose two sublayers have a norm each).
 // grid (groups of LSJ_WARPS / WPT tokens, sequences) or (groups of rows); dynamic smem LSJ_WARPS / WPT * W floats.
 constexpr int LSJ_WARPS = 4;
 
@@ -114,7 +116,8 @@ template <typename OT, bool VEC, int WPT>
 __global__ void __launch_bounds__(32 * LSJ_WARPS)
     ls_join_kernel(float* __restrict__ x, const int* __restrict__ q_start, const int* __restrict__ q_len,
                    const int* __restrict__ rows, int n_rows, JoinTerm a, JoinTerm b, JoinTerm c, float eps,
-                   const float* __restrict__ gamma, int gstride, int plus_one, OT* __restrict__ h, int ld_h, int W) {
+                   const float* __restrict__ gamma, int gstride, int plus_one, OT* __restrict__ h, int ld_h, int W,
+                   const float* __restrict__ gamma2, OT* __restrict__ h2, int ld_h2, int replace) {
   pdl_begin();
   extern __shared__ __align__(16) float sm[];
   __shared__ float red[32];
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(32 * LSJ_WARPS)
   float* xr = x + static_cast<size_t>(t) * W;
   float ss = 0.f;
   for (int i = lane; i < nv; i += NL) {
-    float4 v = Ld4<VEC>::ld(xr, i);
+    float4 v = replace ? make_float4(0.f, 0.f, 0.f, 0.f) : Ld4<VEC>::ld(xr, i);
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
       if (terms[k].y == nullptr) continue;
@@ -171,20 +174,30 @@ __global__ void __launch_bounds__(32 * LSJ_WARPS)
     if (rows == nullptr) Ld4<VEC>::st(xr, i, v);
   }
   if (h == nullptr) return;
-  const float rn = 1.f / sqrtf(total(ss) * inv_w + eps);   // (the block barriers inside also order xs for WPT > 1)
+  // gamma == nullptr: the operand is the residual row itself (no norm)
+  const float tot = total(ss);                             // (the block barriers inside also order xs for WPT > 1)
+  const float rn = gamma != nullptr ? 1.f / sqrtf(tot * inv_w + eps) : 1.f;
   const float one = plus_one ? 1.f : 0.f;
-  const float g0 = gamma[0] + one;
+  const float g0 = gamma != nullptr ? gamma[0] + one : 1.f;
   OT* hr = h + static_cast<size_t>(hrow) * ld_h;
+  OT* hr2 = h2 != nullptr ? h2 + static_cast<size_t>(hrow) * ld_h2 : nullptr;
   __syncwarp();
   for (int i = lane; i < nv; i += NL) {
-    float4 v = Ld4<VEC>::ld(xs, i);
+    const float4 xv = Ld4<VEC>::ld(xs, i);
     float4 g = make_float4(g0, g0, g0, g0);
     if (gstride) {
       g = Ld4<VEC>::ld(gamma, i);
       g.x += one; g.y += one; g.z += one; g.w += one;
     }
+    float4 v = xv;
     v.x *= rn * g.x; v.y *= rn * g.y; v.z *= rn * g.z; v.w *= rn * g.w;
     st_operand(hr, i, v, VEC);
+    if (hr2 != nullptr) {                                  // a second norm of the same row (its own gains, always a vector)
+      g = Ld4<VEC>::ld(gamma2, i);
+      v = xv;
+      v.x *= rn * (g.x + one); v.y *= rn * (g.y + one); v.z *= rn * (g.z + one); v.w *= rn * (g.w + one);
+      st_operand(hr2, i, v, VEC);
+    }
   }
 }
 
@@ -311,7 +324,9 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const float* q, const
 }
 
 // ------------------------------------------------------------------------------------------ softmax attention
-// out[t, h, :] = sum_j softmax_j(q_t . k_j * scale) v_j over the keys j <= i, and j > i - window when window > 0.
+// out[t, h, :] = sum_j softmax_j(q_t . k_j * scale) v_j over the keys j <= i, and j > i - window when window > 0
+// (the first keep_first keys stay visible whatever the window).  softcap > 0: score <- softcap * tanh(score / softcap).
+// sink [H] (optional): exp(sink_h) joins the denominator of head h; it has no key and no value.
 // Positions count from the start of the sequence: i = kv_len - q_len + index in span.  One warp per (query, head): a
 // pass over 32 keys computes one score per lane, rescales the running sums, then the lanes own value channels.
 // grid (query tiles of 4, heads, sequences), 128 threads, dynamic smem 4 * D floats.
@@ -331,7 +346,8 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
     softmax_attention_kernel(const float* __restrict__ q, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
                              OT* __restrict__ out, int ld_out, const int* __restrict__ block_table, int max_pages,
                              const int* __restrict__ q_start, const int* __restrict__ q_len,
-                             const int* __restrict__ kv_len, int H, int G, int D, int V, int window, float scale, int ldv) {
+                             const int* __restrict__ kv_len, int H, int G, int D, int V, int window, float scale, int ldv,
+                             float softcap, int keep_first, const float* __restrict__ sink) {
   pdl_begin();
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -357,32 +373,44 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
   float acc[VR];
 #pragma unroll
   for (int r = 0; r < VR; ++r) acc[r] = 0.f;
+  // sink: a learned score per head that takes part in the denominator only (a key whose value is zero); it starts the
+  // running maximum and sum of ONE warp of the query
   float mx = -INFINITY, den = 0.f;
+  if (sink != nullptr && (WPQ == 1 || warp == 0)) {
+    mx = sink[hd];
+    den = 1.f;
+  }
   const int stride = WPQ > 1 ? 32 * WPQ : 32;
-  for (int j0 = lo + (WPQ > 1 ? 32 * warp : 0); j0 <= pi; j0 += stride) {
-    const int j = j0 + lane;
-    float sc = -INFINITY;
-    long long slot = 0;
-    if (j <= pi) {
-      slot = static_cast<long long>(bt[j >> 6]) * 64 + (j & 63);
-      sc = dot_row<CT>(qs, k_cache + (static_cast<size_t>(slot) * G + g) * D, D, kvec);
-    }
-    const float nmx = fmaxf(mx, warp_max_(sc));        // finite: key j0 is always visible
-    const float corr = expf(mx - nmx);                 // first pass: exp(-inf) = 0
-    const float p = (j <= pi) ? expf(sc - nmx) : 0.f;
-    den = den * corr + warp_sum_(p);
-    mx = nmx;
+  // visible keys: [0, kf) -- the first keep_first keys, kept in sight when the window has moved past them -- and [lo, pi]
+  const int kf = min(keep_first, lo);
+  for (int seg = kf > 0 ? 0 : 1; seg < 2; ++seg) {
+    const int jbeg = seg == 0 ? 0 : lo, jend = seg == 0 ? kf - 1 : pi;
+    for (int j0 = jbeg + (WPQ > 1 ? 32 * warp : 0); j0 <= jend; j0 += stride) {
+      const int j = j0 + lane;
+      float sc = -INFINITY;
+      long long slot = 0;
+      if (j <= jend) {
+        slot = static_cast<long long>(bt[j >> 6]) * 64 + (j & 63);
+        sc = dot_row<CT>(qs, k_cache + (static_cast<size_t>(slot) * G + g) * D, D, kvec);
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+      }
+      const float nmx = fmaxf(mx, warp_max_(sc));        // finite: key j0 is always visible
+      const float corr = expf(mx - nmx);                 // first pass: exp(-inf) = 0
+      const float p = (j <= jend) ? expf(sc - nmx) : 0.f;
+      den = den * corr + warp_sum_(p);
+      mx = nmx;
 #pragma unroll
-    for (int r = 0; r < VR; ++r) acc[r] *= corr;
-    const int cnt = min(32, pi - j0 + 1);
-    for (int jj = 0; jj < cnt; ++jj) {
-      const float w = __shfl_sync(0xffffffffu, p, jj);
-      const long long sl = __shfl_sync(0xffffffffu, slot, jj);
-      const CT* vrow = v_cache + static_cast<size_t>(sl) * ldv + g * V;
+      for (int r = 0; r < VR; ++r) acc[r] *= corr;
+      const int cnt = min(32, jend - j0 + 1);
+      for (int jj = 0; jj < cnt; ++jj) {
+        const float w = __shfl_sync(0xffffffffu, p, jj);
+        const long long sl = __shfl_sync(0xffffffffu, slot, jj);
+        const CT* vrow = v_cache + static_cast<size_t>(sl) * ldv + g * V;
 #pragma unroll
-      for (int r = 0; r < VR; ++r) {
-        const int d = lane + 32 * r;
-        if (d < V) acc[r] += w * ldf(vrow, d);
+        for (int r = 0; r < VR; ++r) {
+          const int d = lane + 32 * r;
+          if (d < V) acc[r] += w * ldf(vrow, d);
+        }
       }
     }
   }
@@ -450,7 +478,8 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
                                  const bf16* __restrict__ v_cache, bf16* __restrict__ out, int ld_out,
                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
                                  const int* __restrict__ q_len, const int* __restrict__ kv_len, int H, int G, int D,
-                                 int V, int window, float scale, int ldv, int hg) {
+                                 int V, int window, float scale, int ldv, int hg, float softcap, int keep_first,
+                                 const float* __restrict__ sink) {
   // hg == 1: a block = 64 consecutive queries of one head (blockIdx.y).  hg > 1 (= H / G): the hg query heads that share
   // key/value head blockIdx.y are stacked into the rows of the tile, row r = (query r / hg, head r % hg of the group), so a
   // page is staged once for all of them and a decode step of one sequence fills hg rows instead of one.
@@ -498,8 +527,18 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
 #pragma unroll
   for (int vt = 0; vt < 2 * VT; ++vt) oacc[vt][0] = oacc[vt][1] = oacc[vt][2] = oacc[vt][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  if (sink != nullptr) {                           // the sink starts the running maximum; its weight 1 sits in one lane of the quad
+    m0 = sink[hd0];
+    m1 = sink[hd1];
+    l0 = l1 = tig == 0 ? 1.f : 0.f;
+  }
   const int* bt = block_table + static_cast<size_t>(s) * max_pages;
-  for (int pg = lo_min >> 6; pg <= (pmax >> 6); ++pg) {
+  // pages of the kept first keys that lie in front of the window's pages, then the window's pages
+  const int pg_lo = lo_min >> 6;
+  const int n_pre = (window > 0 && keep_first > 0) ? min((keep_first - 1) >> 6, pg_lo - 1) + 1 : 0;
+  const int n_it = n_pre + (pmax >> 6) - pg_lo + 1;
+  for (int it = 0; it < n_it; ++it) {
+    const int pg = it < n_pre ? it : pg_lo + it - n_pre;
     const size_t page = static_cast<size_t>(bt[pg]);
     const int kb = pg * 64;
     __syncthreads();                           // every warp is done with the previous tile
@@ -523,7 +562,7 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
       }
     }
     __syncthreads();
-    if (!wact || kb > wpmax || kb + 63 < wlo) continue;      // warp-uniform: no key of this page is visible to the warp
+    if (!wact || kb > wpmax || (kb + 63 < wlo && kb >= keep_first)) continue;      // warp-uniform: no key of this page is visible to the warp
     float sc[8][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
@@ -541,10 +580,14 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
       const int j0 = kb + nt * 8 + 2 * tig, j1 = j0 + 1;
-      sc[nt][0] = (ok0 && j0 >= lo0 && j0 <= p0) ? sc[nt][0] : -INFINITY;
-      sc[nt][1] = (ok0 && j1 >= lo0 && j1 <= p0) ? sc[nt][1] : -INFINITY;
-      sc[nt][2] = (ok1 && j0 >= lo1 && j0 <= p1) ? sc[nt][2] : -INFINITY;
-      sc[nt][3] = (ok1 && j1 >= lo1 && j1 <= p1) ? sc[nt][3] : -INFINITY;
+      if (softcap > 0.f) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nt][e] = softcap * tanhf(sc[nt][e] / softcap);
+      }
+      sc[nt][0] = (ok0 && (j0 >= lo0 || j0 < keep_first) && j0 <= p0) ? sc[nt][0] : -INFINITY;
+      sc[nt][1] = (ok0 && (j1 >= lo0 || j1 < keep_first) && j1 <= p0) ? sc[nt][1] : -INFINITY;
+      sc[nt][2] = (ok1 && (j0 >= lo1 || j0 < keep_first) && j0 <= p1) ? sc[nt][2] : -INFINITY;
+      sc[nt][3] = (ok1 && (j1 >= lo1 || j1 < keep_first) && j1 <= p1) ? sc[nt][3] : -INFINITY;
       tm0 = fmaxf(tm0, fmaxf(sc[nt][0], sc[nt][1]));
       tm1 = fmaxf(tm1, fmaxf(sc[nt][2], sc[nt][3]));
     }
@@ -1144,7 +1187,8 @@ inline int last_error() { return static_cast<int>(cudaGetLastError()); }
 int launch_ls_join(float* x, const int* q_start, const int* q_len, const int* rows, int n_rows, int n_seqs, int max_q,
                    const float* y0, int ld0, const float* w0, int norm0, const float* y1, int ld1, const float* w1,
                    int norm1, const float* y2, int ld2, const float* w2, int norm2, float eps, const float* gamma,
-                   int gstride, int plus_one, void* h, int ld_h, int W, int f32, cudaStream_t s) {
+                   int gstride, int plus_one, void* h, int ld_h, int W, int f32, const float* gamma2, void* h2, int ld_h2,
+                   int replace, cudaStream_t s) {
   const bool wide = W > 512;                 // wide rows: the whole block works on one token
   const int tpb = wide ? 1 : LSJ_WARPS;
   dim3 grid;
@@ -1161,14 +1205,15 @@ int launch_ls_join(float* x, const int* q_start, const int* q_len, const int* ro
   const bool vec = W % 4 == 0 && al16(x) && (y0 == nullptr || (ld0 % 4 == 0 && al16(y0))) &&
                    (y1 == nullptr || (ld1 % 4 == 0 && al16(y1))) && (y2 == nullptr || (ld2 % 4 == 0 && al16(y2))) &&
                    al16(w0) && al16(w1) && al16(w2) && (h == nullptr || (ld_h % 4 == 0 && al16(h))) &&
-                   (gstride == 0 || al16(gamma));
+                   (gstride == 0 || al16(gamma)) && (h2 == nullptr || (ld_h2 % 4 == 0 && al16(h2) && al16(gamma2)));
 #define B2B_LSJ1(OT, VEC, WPT)                                                                                          \
   do {                                                                                                                  \
     if (smem > 48 * 1024)                                                                                               \
       cudaFuncSetAttribute(ls_join_kernel<OT, VEC, WPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
                            static_cast<int>(smem));                                                                     \
     launch_kernel(ls_join_kernel<OT, VEC, WPT>, grid, dim3(32 * LSJ_WARPS), smem, s, 1u, x, q_start, q_len, rows, n_rows, \
-                  a, b, c, eps, gamma, gstride, plus_one, static_cast<OT*>(h), ld_h, W);                                 \
+                  a, b, c, eps, gamma, gstride, plus_one, static_cast<OT*>(h), ld_h, W, gamma2, static_cast<OT*>(h2),    \
+                  ld_h2, replace);                                                                                      \
   } while (0)
 #define B2B_LSJ(OT, VEC)                                                                                                \
   do {                                                                                                                  \
@@ -1214,8 +1259,10 @@ int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int of
 int launch_softmax_attention(const float* q, const void* k_cache, const void* v_cache, void* out, int ld_out,
                              const int* block_table, int max_pages, const int* q_start, const int* q_len,
                              const int* kv_len, int n_seqs, int max_q, int H, int G, int D, int V, int window,
-                             float scale, int ldv, int f32, cudaStream_t s) {
+                             float scale, int ldv, int f32, float softcap, int keep_first, const float* sink,
+                             cudaStream_t s) {
   if (n_seqs <= 0 || max_q <= 0) return 0;
+  if (window <= 0) keep_first = 0;          // every earlier key is visible anyway
   if (V > 64 * SMX_VR || G <= 0 || H % G != 0) return -2;
   const bool wide_v = V > 32 * SMX_VR;      // values of 257 .. 512 channels: 16 channels per lane
   if (ldv <= 0) ldv = G * V;               // values in a cache of their own; otherwise a view into wider rows
@@ -1231,7 +1278,7 @@ int launch_softmax_attention(const float* q, const void* k_cache, const void* v_
   if (dts == A && vts == B)                                                                                             \
     launch_kernel(softmax_attention_mma_kernel<A, B>, dim3(mgrid), dim3(32 * SMX_MMA_WARPS), 0, s, 1u, q,                              \
                   static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out), ld_out,  \
-                  block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale, ldv, hg);
+                  block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale, ldv, hg, softcap, keep_first, sink);
 #define B2B_SMXROW(A) B2B_SMXMMA(A, 2) B2B_SMXMMA(A, 4) B2B_SMXMMA(A, 5) B2B_SMXMMA(A, 6) B2B_SMXMMA(A, 8)
     B2B_SMXROW(2) B2B_SMXROW(4) B2B_SMXROW(6) B2B_SMXROW(8)
 #undef B2B_SMXROW
@@ -1241,7 +1288,7 @@ int launch_softmax_attention(const float* q, const void* k_cache, const void* v_
 #define B2B_SMX(CT, WPQ, VR_, GRID, BLOCK, SMEM)                                                                         \
   launch_kernel(softmax_attention_kernel<CT, CT, WPQ, VR_>, dim3(GRID), dim3(BLOCK), SMEM, s, 1u, q,                     \
                 static_cast<const CT*>(k_cache), static_cast<const CT*>(v_cache), static_cast<CT*>(out), ld_out,        \
-                block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale, ldv)
+                block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale, ldv, softcap, keep_first, sink)
 #define B2B_SMX_T(WPQ, GRID, BLOCK, SMEM)                                                                               \
   if (f32) {                                                                                                            \
     if (wide_v) B2B_SMX(float, WPQ, 2 * SMX_VR, GRID, BLOCK, SMEM);                                                     \
