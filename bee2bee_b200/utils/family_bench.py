@@ -1,7 +1,8 @@
 """Side-by-side throughput of two model families at equal size (``bench.py --families``): the hybrid Kepovik graph
 next to the closest uniform decoder (Llama), or (``--family repudra``) the parallel-block Repudra graph next to the
 closest hybrid (Kepovik), or (``--family lonulix``) the post-norm Lonulix graph next to Repudra (the other family whose
-attention and recurrences run on the kernels of ``csrc/seqmix.cu``); random weights, layer shapes of real models.
+attention and recurrences run on the kernels of ``csrc/seqmix.cu``), or (``--family fisopel``) the looped Fisopel graph next
+to Lonulix (the other family with latent attention and routed experts); random weights, layer shapes of real models.
 
 Per width it reports (1) prefill and decode tokens/s through the same ``GpuRunner`` calls that serving uses (chunked
 graph prefill, CUDA-graph decode steps), timed with CUDA events, and (2) a per-kernel breakdown of one eager prefill
@@ -98,6 +99,39 @@ def lonulix_sized(width: int, vocab: int = 32000) -> ModelConfig:
                        max_position=1 << 30, norm="rms", norm_eps=1e-6, act="silu", glu=True, rope_theta=0.0,
                        embed_scale=2.0, layer_specs=specs, block_layout="post_norm", norm_groups=4, skip_scale=2.0,
                        gated_residual=True)
+
+
+def fisopel_sized(width: int, vocab: int = 32000) -> ModelConfig:
+    """four parallel-block layers, the middle two run twice (six layer runs, as many as the six-layer models above):
+    attention (width / 128 heads of 128 channels, grouped 4:1, per-head q / k norm, scores capped at 50, window 1024 with 64
+    kept first keys, sink), gated latent attention (width / 128 heads of 64 plain + 32 rotated query/key channels and 128
+    value channels over a cached latent of 96 channels, YaRN x 4), attention, latent attention; every layer has 8 gated
+    experts of 3 width / 8 hidden channels (2 per token) beside a shared one of the same size.  The layer matrices hold
+    about 53 width^2 parameters, as ``lonulix_sized(width)`` does."""
+    H = width // 128
+    eff = max(128, (3 * width // 8) // 128 * 128)
+
+    def routed(sp):
+        sp.ff_kind, sp.experts, sp.expert_ff, sp.top, sp.shared_ff = "moe", 8, eff, 2, eff
+        sp.route_kind, sp.expert_gated, sp.ff = "logit_topk", True, 9 * eff
+        return sp
+
+    def att():
+        return routed(LayerSpec(mixer="softmax_attention", heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128,
+                                scale=128 ** -0.5, window=1024, keep_first=64, softcap=50.0, qk_norm="head", v_norm=False,
+                                sink=True))
+
+    def latt():
+        rot = RotarySpec(dims=32, base=10000.0, factor=4.0, original=2048, half=True)
+        return routed(LayerSpec(mixer="latent_attention", heads=H, kv_heads=1, dim=64, vdim=128, scale=96 ** -0.5, rot=rot,
+                                q_rank=0, kv_rank=96, rot_dim=32, out_gate=True))
+
+    specs = (att(), latt(), att(), latt())
+    return ModelConfig(name=f"mini-fisopel-{width}", family="fisopel", vocab_size=vocab, hidden_size=width,
+                       n_layers=len(specs), n_heads=H, n_kv_heads=max(1, H // 4), head_dim=128,
+                       ffn_size=max(sp.ff for sp in specs), max_position=1 << 30, norm="rms", norm_eps=1e-5, act="silu",
+                       glu=True, rope_theta=0.0, tie_embeddings=True, embed_scale=2.0, layer_specs=specs,
+                       block_layout="parallel", ff_norm=True, loop_start=1, loop_stop=3, loop_times=2, loop_in=True)
 
 
 def llama_sized(width: int, layer_params: int, n_layers: int = 4, vocab: int = 32000) -> ModelConfig:
@@ -251,10 +285,14 @@ def cost(name: str, a, hint: Dict):
     if name == "rot_heads":
         return 0.0, 2 * T * a[3] * a[4] * 4, False
     if name == "moe_route":
-        return 0.0, T * (a[2].numel() + a[3] + 1) * 4, False
+        return 0.0, T * (a[3] + a[4] + 1) * 4, False
     if name == "gated_cols":
         n = a[6]
-        return 0.0, T * n * ((4 if a[3] is not None else 8) + a[5].element_size()), False
+        return 0.0, T * n * ((4 if (a[3] is not None and not a[9]) else 8) + a[5].element_size()), False
+    if name == "head_up_gate":
+        Tn, H, V, C = a[5], a[6], a[7], a[8]
+        elt = a[0].element_size()
+        return 2.0 * Tn * H * V * C, Tn * H * C * elt + H * V * C * elt + Tn * H * V * ((4 if a[2] is not None else 0) + elt), False
     if name in ("rmsnorm", "layernorm", "add"):
         return 0.0, 3 * _nb(a[0]), False
     if name == "embed":
@@ -384,7 +422,9 @@ def run(widths, prompt_len=2048, batch=32, steps=32, warmup=3, ctx=512, device="
     out = []
     for w in widths:
         kep = kepovik_sized(w)
-        if family == "lonulix":
+        if family == "fisopel":
+            pair = (fisopel_sized(w), lonulix_sized(w))
+        elif family == "lonulix":
             pair = (lonulix_sized(w), repudra_sized(w))
         else:
             pair = (repudra_sized(w), kep) if family == "repudra" else (kep, llama_sized(w, layer_params(kep)))

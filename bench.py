@@ -61,10 +61,12 @@ def parse_args():
                     help="side-by-side run instead of the headline: the hybrid Kepovik graph next to a Llama of equal size "
                          "at these widths (comma separated, e.g. 1024,2048,4096): prefill / decode tokens/s and a per-kernel "
                          "roofline table, one JSON line per model (bee2bee_b200/utils/family_bench.py)")
-    ap.add_argument("--family", default="kepovik", choices=["kepovik", "repudra", "lonulix"],
+    ap.add_argument("--family", default="kepovik", choices=["kepovik", "repudra", "lonulix", "fisopel"],
                     help="with --families: kepovik = Kepovik next to a Llama of equal size (default); repudra = the "
                          "parallel-block Repudra graph next to a Kepovik of equal size; lonulix = the post-norm Lonulix "
-                         "graph (latent attention, HGRN2, routed experts) next to a Repudra of equal size")
+                         "graph (latent attention, HGRN2, routed experts) next to a Repudra of equal size; fisopel = the looped "
+                         "Fisopel graph (attention with sink and kept first keys, gated latent attention, gated experts) "
+                         "next to a Lonulix of equal size")
     a = ap.parse_args()
     cfg = CONFIGS[a.config]
     dflt = dict(model="llama-3-8b", dtype="bf16", batch=32, groups=0, prompt_len=16, steps=64, warmup=8)
