@@ -411,7 +411,8 @@ __global__ void __launch_bounds__(256)
 // value up-projection of latent attention, applied to the attention output taken over the latents), so this is a batch
 // of H small matrix products.  gate (optional) = sigmoid of column off_g + h * V + v of an fp32 row (the output gate of the
 // concatenated heads).  A block = 64 tokens x 64 value channels of one head, 256 threads with 4 x 4 outputs each, the
-// latent dimension walked in slices of 16 through shared memory; fp32 accumulation.
+// latent dimension walked in slices of 16 through shared memory; fp32 accumulation.  (float32 mode and odd shapes; the
+// bf16 serving mode runs the tensor-core variant below.)
 template <typename OT>
 __global__ void __launch_bounds__(256)
     head_up_gate_kernel(const OT* __restrict__ a, int ld_a, const OT* __restrict__ U, const float* __restrict__ gate,
@@ -470,6 +471,93 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// bf16 operands with a latent width that is a multiple of 16: the same tile on `mma.sync.m16n8k16` tensor cores.  A block =
+// 64 tokens x 64 value channels of one head, a warp = 16 tokens x 64 channels (8 accumulator tiles).  The [64, C] slices of
+// the latent rows and of U are staged in shared memory with 16-byte loads, 128 latent channels at a time (row stride + 8
+// elements: the fragment loads of a warp fall into 32 different banks).
+__device__ __forceinline__ void mma_bf16_16816_(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+constexpr int HUG_KC = 128, HUG_KS = HUG_KC + 8;
+__global__ void __launch_bounds__(128)
+    head_up_gate_mma_kernel(const bf16* __restrict__ a, int ld_a, const bf16* __restrict__ U,
+                            const float* __restrict__ gate, int ld_g, int off_g, bf16* __restrict__ out, int ld_out, int T,
+                            int H, int V, int C) {
+  pdl_begin();
+  __shared__ __align__(16) bf16 stage[2 * 64 * HUG_KS];      // operand slices; the epilogue tile takes their place
+  bf16* As = stage;
+  bf16* Us = stage + 64 * HUG_KS;
+  const int h = blockIdx.z, v0 = blockIdx.y * 64, t0 = blockIdx.x * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  float acc[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  for (int c0 = 0; c0 < C; c0 += HUG_KC) {
+    const int kc = min(HUG_KC, C - c0), n8 = kc >> 3;          // (C is a multiple of 16)
+    if (c0 > 0) __syncthreads();
+    for (int idx = threadIdx.x; idx < 64 * n8; idx += 128) {
+      const int r = idx / n8, c8 = idx - r * n8;
+      uint4 av = make_uint4(0u, 0u, 0u, 0u), uv = make_uint4(0u, 0u, 0u, 0u);
+      if (t0 + r < T) av = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(t0 + r) * ld_a + static_cast<size_t>(h) * C + c0 + c8 * 8);
+      if (v0 + r < V) uv = *reinterpret_cast<const uint4*>(U + (static_cast<size_t>(h) * V + v0 + r) * C + c0 + c8 * 8);
+      *reinterpret_cast<uint4*>(As + r * HUG_KS + c8 * 8) = av;
+      *reinterpret_cast<uint4*>(Us + r * HUG_KS + c8 * 8) = uv;
+    }
+    __syncthreads();
+    const bf16* ar = As + (warp * 16 + gid) * HUG_KS + 2 * tig;
+    const bf16* ur = Us + gid * HUG_KS + 2 * tig;
+    for (int k0 = 0; k0 < kc; k0 += 16) {
+      unsigned af[4];
+      af[0] = *reinterpret_cast<const unsigned*>(ar + k0);
+      af[1] = *reinterpret_cast<const unsigned*>(ar + 8 * HUG_KS + k0);
+      af[2] = *reinterpret_cast<const unsigned*>(ar + k0 + 8);
+      af[3] = *reinterpret_cast<const unsigned*>(ar + 8 * HUG_KS + k0 + 8);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const unsigned b0 = *reinterpret_cast<const unsigned*>(ur + nt * 8 * HUG_KS + k0);
+        const unsigned b1 = *reinterpret_cast<const unsigned*>(ur + nt * 8 * HUG_KS + k0 + 8);
+        mma_bf16_16816_(acc[nt], af, b0, b1);
+      }
+    }
+  }
+  // epilogue through shared memory: a warp parks its 16 x 64 tile, then walks it row by row so that the gate is read and
+  // the operand written in whole 256- and 128-byte rows (a lane owns two adjacent channels; V is even)
+  static_assert(sizeof(float) * 4 * 16 * (64 + 8) <= sizeof(bf16) * 2 * 64 * HUG_KS, "epilogue tile fits the staging area");
+  float (*tile)[16][64 + 8] = reinterpret_cast<float (*)[16][64 + 8]>(stage);
+  __syncthreads();                                   // every warp is done with the operand slices
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    *reinterpret_cast<float2*>(&tile[warp][gid][nt * 8 + 2 * tig]) = make_float2(acc[nt][0], acc[nt][1]);
+    *reinterpret_cast<float2*>(&tile[warp][gid + 8][nt * 8 + 2 * tig]) = make_float2(acc[nt][2], acc[nt][3]);
+  }
+  __syncwarp();
+  const int v = v0 + 2 * lane;
+  if (v >= V) return;
+  const int rb = blockIdx.x * 64 + warp * 16;
+  float2 gv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {                      // all gate loads of the warp's rows in flight at once
+    gv[i] = make_float2(0.f, 0.f);
+    if (gate != nullptr && rb + i < T) {
+      const float* g = gate + static_cast<size_t>(rb + i) * ld_g + off_g + h * V + v;
+      gv[i] = make_float2(g[0], g[1]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (rb + i >= T) continue;
+    float2 o = *reinterpret_cast<const float2*>(&tile[warp][i][2 * lane]);
+    if (gate != nullptr) {
+      o.x *= sigmoid_(gv[i].x);
+      o.y *= sigmoid_(gv[i].y);
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + static_cast<size_t>(rb + i) * ld_out + h * V + v) = __floats2bfloat162_rn(o.x, o.y);
+  }
+}
+
 inline int last_error() { return static_cast<int>(cudaGetLastError()); }
 
 }  // namespace
@@ -479,6 +567,12 @@ int launch_head_up_gate(const void* a, int ld_a, const void* U, const float* gat
   if (T <= 0 || H <= 0 || V <= 0) return 0;
   if (C <= 0 || H > 65535) return -2;
   const dim3 grid((T + 63) / 64, (V + 63) / 64, H);
+  if (!f32 && C % 16 == 0 && V % 2 == 0 && ld_a % 8 == 0 && ld_out % 2 == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(U) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0) {
+    launch_kernel(head_up_gate_mma_kernel, grid, dim3(128), 0, s, 1u, static_cast<const bf16*>(a), ld_a,
+                  static_cast<const bf16*>(U), gate, ld_g, off_g, static_cast<bf16*>(out), ld_out, T, H, V, C);
+    return last_error();
+  }
   if (f32)
     launch_kernel(head_up_gate_kernel<float>, grid, dim3(256), 0, s, 1u, static_cast<const float*>(a), ld_a,
                   static_cast<const float*>(U), gate, ld_g, off_g, static_cast<float*>(out), ld_out, T, H, V, C);

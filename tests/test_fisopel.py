@@ -454,7 +454,8 @@ def test_gated_columns_with_expert_weights(lead, per, E):
 
 
 @gpu
-@pytest.mark.parametrize("T,H,V,C", [(1, 3, 24, 24), (70, 6, 48, 128), (130, 2, 65, 33), (5, 16, 8, 16)])
+@pytest.mark.parametrize("T,H,V,C", [(1, 3, 24, 24), (70, 6, 48, 128), (130, 2, 65, 33), (5, 16, 8, 16), (200, 4, 40, 96),
+                                     (64, 2, 130, 32)])       # latent widths in multiples of 16 take the tensor-core variant in bf16
 def test_per_head_up_projection_with_gate(T, H, V, C):
     from bee2bee_b200 import ops
 
