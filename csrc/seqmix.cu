@@ -1268,7 +1268,10 @@ int launch_softmax_attention(const float* q, const void* k_cache, const void* v_
   if (ldv <= 0) ldv = G * V;               // values in a cache of their own; otherwise a view into wider rows
   // short spans and decode steps of grouped heads: the heads that share a key/value head become rows of the tile
   const int hg = (H / G > 1 && max_q < 16 * SMX_MMA_WARPS) ? H / G : 1;
-  if (!f32 && max_q * hg >= SMX_MMA_MIN_Q && D % 8 == 0 && V % 8 == 0 && D <= 128 && V <= 128 && ld_out % 2 == 0 &&
+  // (decode steps of 4 or more grouped heads too when sequences x key/value heads fill the machine: a page is staged once
+  // per key/value head instead of once per query head -- 32 sequences x 8 key/value heads of 128 channels at 512 keys: 6 %
+  // off the decode step; with 2 key/value heads the 64 blocks that walk their pages one by one lose to the 8-warp kernel)
+  if (!f32 && (max_q * hg >= SMX_MMA_MIN_Q || (hg >= 4 && max_q <= SMX_DEC_MAX_Q && n_seqs * G >= 256)) && D % 8 == 0 && V % 8 == 0 && D <= 128 && V <= 128 && ld_out % 2 == 0 &&
       ldv % 8 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 16 == 0) {
     dim3 mgrid((max_q * hg + 16 * SMX_MMA_WARPS - 1) / (16 * SMX_MMA_WARPS), hg > 1 ? G : H, n_seqs);
     const int dt = (D + 15) / 16, vt = (V + 15) / 16;
