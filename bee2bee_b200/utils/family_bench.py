@@ -103,7 +103,7 @@ def lonulix_sized(width: int, vocab: int = 32000) -> ModelConfig:
 
 def fisopel_sized(width: int, vocab: int = 32000) -> ModelConfig:
     """four parallel-block layers, the middle two run twice (six layer runs, as many as the six-layer models above):
-    attention (width / 128 heads of 128 channels, grouped 4:1, per-head q / k norm, scores capped at 50, window 1024 with 64
+    attention (width / 128 heads of 128 channels, grouped 4:1, per-head q / k norm, scores capped at 30, window 1024 with 64
     kept first keys, sink), gated latent attention (width / 128 heads of 64 plain + 32 rotated query/key channels and 128
     value channels over a cached latent of 96 channels, YaRN x 4), attention, latent attention; every layer has 8 gated
     experts of 3 width / 8 hidden channels (2 per token) beside a shared one of the same size.  The layer matrices hold
@@ -118,7 +118,7 @@ def fisopel_sized(width: int, vocab: int = 32000) -> ModelConfig:
 
     def att():
         return routed(LayerSpec(mixer="softmax_attention", heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128,
-                                scale=128 ** -0.5, window=1024, keep_first=64, softcap=50.0, qk_norm="head", v_norm=False,
+                                scale=128 ** -0.5, window=1024, keep_first=64, softcap=30.0, qk_norm="head", v_norm=False,
                                 sink=True))
 
     def latt():

@@ -303,7 +303,7 @@ def _paged(rows, page_ids, dtype):
 
 @gpu
 @pytest.mark.parametrize("H,G,D,V,window,keep,cap,nq", [
-    (4, 2, 16, 24, 0, 0, 0.0, 150), (4, 2, 16, 24, 40, 5, 20.0, 150), (8, 2, 48, 32, 70, 66, 50.0, 150),
+    (4, 2, 16, 24, 0, 0, 0.0, 150), (4, 2, 16, 24, 40, 5, 20.0, 150), (8, 4, 40, 24, 70, 66, 25.0, 150),
     (3, 3, 20, 12, 9, 2, 5.0, 150), (4, 1, 32, 32, 64, 64, 30.0, 1), (6, 2, 16, 16, 33, 1, 10.0, 2),
     (4, 4, 64, 64, 100, 130, 15.0, 17), (2, 1, 8, 40, 1, 1, 8.0, 150), (4, 2, 16, 24, 129, 3, 20.0, 9)])
 def test_attention_kernel_cap_kept_keys_and_sink(H, G, D, V, window, keep, cap, nq):
@@ -349,6 +349,38 @@ def test_attention_kernel_cap_kept_keys_and_sink(H, G, D, V, window, keep, cap, 
         s = (q[:, hd].double() @ k[:, hd // (H // G)].double().T) * scale
         plain[:, hd] = O.softmax_with_sink(s, okw, None) @ v[:, hd // (H // G)].double()
     assert torch.allclose(out.cpu().double().view(nq, H, V), plain[n - nq:], atol=2e-5, rtol=2e-5)
+
+
+@gpu
+@pytest.mark.parametrize("window,keep", [(0, 0), (70, 9)])
+def test_attention_decode_steps_of_many_grouped_heads(window, keep):
+    """32 sequences x 8 key/value heads x 4 query heads each, one decoded token per sequence: in bf16 the heads of a group
+    become rows of the tensor-core tile (a page is staged once per key/value head); cap, kept keys and sink as above"""
+    from bee2bee_b200 import ops
+
+    S, H, G, D, V, n, dev, cap = 32, 32, 8, 16, 24, 150, "cuda", 12.0
+    g = torch.Generator().manual_seed(window)
+    q = torch.randn(S, H, D, generator=g) * 1.5
+    k, v = torch.randn(n, G, D, generator=g), torch.randn(n, G, V, generator=g)
+    sink = torch.randn(H, generator=g) * 2.0
+    scale = 2.0 * D ** -0.5
+    ok = O.visible(n, window, keep)[n - 1:n]
+    want = torch.zeros(S, H, V, dtype=torch.float64)
+    for hd in range(H):
+        sc = cap * torch.tanh((q[:, hd].double() @ k[:, hd // (H // G)].double().T) * scale / cap)
+        want[:, hd] = O.softmax_with_sink(sc, ok.expand(S, n), sink[hd].double()) @ v[:, hd // (H // G)].double()
+    pages = [4, 1, 6]
+    bt = torch.tensor([pages + [0] * 5] * S, dtype=torch.int32, device=dev)         # every sequence reads the same pages
+    qs = torch.arange(S, dtype=torch.int32, device=dev)
+    ql = torch.ones(S, dtype=torch.int32, device=dev)
+    kvl = torch.full((S,), n, dtype=torch.int32, device=dev)
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 4e-2)):
+        kc, vc = _paged(k, pages, dtype), _paged(v, pages, dtype)
+        out = torch.zeros(S, H * V, device=dev, dtype=dtype)
+        ops.softmax_attention(q.reshape(S, H * D).to(dev).contiguous(), kc, vc, out, bt, qs, ql, kvl, S, 1, H, G, D, V, window,
+                              scale, softcap=cap, keep_first=keep, sink=sink.to(dev))
+        got = out.float().cpu().double().view(S, H, V)
+        assert torch.allclose(got, want, atol=tol, rtol=tol), float((got - want).abs().max())
 
 
 @gpu
@@ -432,7 +464,7 @@ def test_router_kernel_on_logits(E, top):
 
 
 @gpu
-@pytest.mark.parametrize("lead,per,E", [(40, 24, 5), (0, 16, 3), (6, 5, 4), (96, 64, 12)])
+@pytest.mark.parametrize("lead,per,E", [(40, 24, 5), (0, 16, 3), (6, 5, 4), (80, 48, 10)])
 def test_gated_columns_with_expert_weights(lead, per, E):
     """silu(gate) * up * weight over [shared | expert 0 | expert 1 ...]: weight 1 in front, the token's weight per expert"""
     from bee2bee_b200 import ops
@@ -484,7 +516,7 @@ SINGLE = {
     "latent": lambda: make_cfg([latt()]),
     "latent_yarn": lambda: make_cfg([latt(rot=16, yarn=(4.0, 32, 8.0, 1.0))]),
     "latent_part_rotated": lambda: make_cfg([latt(rot=12, rdims=8, kv_rank=20)]),
-    "latent_wide": lambda: make_cfg([latt(heads=2, dim=32, rot=32, vdim=48, kv_rank=128, yarn=(2.0, 64, 32.0, 1.0))]),
+    "latent_wide": lambda: make_cfg([latt(heads=2, dim=24, rot=16, vdim=40, kv_rank=144, yarn=(3.0, 64, 16.0, 1.0))]),
     "latent_no_rotation": lambda: make_cfg([latt(rot=0)]),
     "experts": lambda: make_cfg([att(cap=0.0, mlp=moe())]),
     "experts_no_shared_top1": lambda: make_cfg([latt(mlp=moe(experts=3, top=1, shared=0))]),
