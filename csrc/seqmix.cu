@@ -1,11 +1,14 @@
 // Sequence mixers of the parallel-block hybrid decoders (Repudra) and the glue around them:
 //
 //   * ls_join            one residual stream: x += sum_k w_k * (optionally width-normed) y_k, then the RMS norm of the
-//                        next block (one gain for all coordinates, or a vector) written as the GEMM operand
+//                        next block (one gain for all coordinates, or a vector) written as the GEMM operand; optionally a
+//                        second normed operand with its own weights (a norm per sublayer of a parallel block), a replace
+//                        mode (the residual entering a pass of a looped range of layers) and a plain operand copy
 //   * rot_attn_prep      softmax attention: RMS norm over the WHOLE q / k projection, rotary positions on the first
 //                        `rdims` channels of every head (pairs 2i, 2i+1; frequencies from a table, so any scaling rule
 //                        is a host matter), per-head value norm, K / V rows into the paged cache
-//   * softmax_attention  causal softmax attention over the paged cache, key width != value width, grouped heads; an
+//   * softmax_attention  causal softmax attention over the paged cache, key width != value width, grouped heads, optional
+//                        window with kept first keys, optional score cap, optional sink in the denominator; an
 //                        exact CUDA-core kernel (one warp per query and head, online softmax) and a tensor-core kernel
 //                        for spans in the bf16 mode
 //   * short_conv         causal per-channel convolution over time + silu, with the last taps-1 inputs per sequence slot
