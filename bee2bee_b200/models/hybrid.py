@@ -414,8 +414,7 @@ class HybridPiece:
         qa = torch.cat([wq[:, D:][:, perm], torch.einsum("hdc,hdw->hcw", uk, wq[:, :D])], 1)     # [H, R + C, W]
         kv = torch.cat([dkv[:C], dkv[C:][perm]], 0)
         mx.f["dkv.norm"] = tensors[q + "dkv.norm"].to(device=dev, dtype=torch.float32).contiguous()
-        freq = sp.rot.frequencies() if rd else [0.0]
-        mx.f["freq"] = torch.tensor(freq, dtype=f64).to(device=dev, dtype=torch.float32)
+        mx.f["freq"], mx.f["freq_lo"] = ops.split_frequencies(sp.rot.frequencies() if rd else [0.0], dev)
         mx.amp = sp.rot.amplitude if rd else 1.0
         mx.w_uv = tensors[q + "uv"].to(device=dev, dtype=torch.float32).view(H, V, C).to(self.dtype).contiguous()
         rows = [("qa", qa.reshape(H * (R + C), W)), ("dkv", kv)]
@@ -566,7 +565,7 @@ class HybridPiece:
             mx.rank = Q
             mx.f["dq.norm"], mx.f["dkv.norm"] = vec(q + "dq.norm"), vec(q + "dkv.norm")
             freq = sp.rot.frequencies() if sp.rot is not None and sp.rot.dims > 0 else [0.0]
-            mx.f["freq"] = torch.tensor(freq, dtype=f64).to(device=dev, dtype=torch.float32)
+            mx.f["freq"], mx.f["freq_lo"] = ops.split_frequencies(freq, dev)
         elif sp.mixer == "hgrn2":
             kd = sp.heads * sp.dim
             rows = [t64(q + "q"), t64(q + "f"), t64(q + "v")]
@@ -662,14 +661,15 @@ class HybridPiece:
         if Q > 0:                       # queries from a normed latent: a second GEMM gives the absorbed query rows
             cq = self._buf(f"cq{Q}", self.dtype, mx.w2.shape[1])[:T]
             ops.latent_prep(proj, mx.off["dq"], Q, mx.off["dkv"], C, R, mx.f["dq.norm"], mx.f["dkv.norm"], mx.f["freq"],
-                            rdims, m.positions, m.slots, cq, kc, self.cfg.norm_eps, T, amp=mx.amp)
+                            rdims, m.positions, m.slots, cq, kc, self.cfg.norm_eps, T, amp=mx.amp, freq_lo=mx.f["freq_lo"])
             qa, off_q = ops.linear(mx.w2, cq, self._buf("qa", torch.float32, mx.w2.shape[0])[:T]), 0
         else:                           # queries straight from the layer input: their absorbed rows are in the fused projection
             ops.latent_prep(proj, 0, 0, mx.off["dkv"], C, R, mx.f["dkv.norm"], mx.f["dkv.norm"], mx.f["freq"], rdims,
-                            m.positions, m.slots, self.h[:T], kc, self.cfg.norm_eps, T, amp=mx.amp)
+                            m.positions, m.slots, self.h[:T], kc, self.cfg.norm_eps, T, amp=mx.amp, freq_lo=mx.f["freq_lo"])
             qa, off_q = proj, mx.off["qa"]
         q = self._buf(f"q{mx.idx}", torch.float32, H * (R + C))[:T]
-        ops.rot_heads(qa, off_q, q, H, R + C, mx.f["freq"], rdims, m.positions, T, slots=m.slots, amp=mx.amp)
+        ops.rot_heads(qa, off_q, q, H, R + C, mx.f["freq"], rdims, m.positions, T, slots=m.slots, amp=mx.amp,
+                      freq_lo=mx.f["freq_lo"])
         ao = self._buf(f"mix{mx.idx}.{H * C}", self.dtype, ops.pad_to(H * C, 64))[:T]
         ops.softmax_attention(q, kc, vc, ao, m.block_table, m.q_start, m.q_len, m.kv_len, m.n_seqs, m.max_q, H, 1, R + C, C,
                               sp.window, sp.scale)

@@ -596,17 +596,27 @@ def post_norm_join(x, *, w, h, y=None, gate=None, off_g=0, gbias=None, idw=None,
                             groups, float(eps), h)
 
 
-def latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, eps, T, amp=1.0):
+def latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, eps, T, amp=1.0,
+                freq_lo=None):
     """latent attention: normed query latent -> ``cq`` (``q_rank`` 0: there is none); cache row ``[rotated shared key part
-    (R) | normed latent (C)]``; ``amp`` multiplies cos and sin"""
+    (R) | normed latent (C)]``; ``amp`` multiplies cos and sin; ``freq_lo``: low parts of the frequencies (``split_frequencies``)"""
     native().latent_prep(proj, off_q, q_rank, off_kv, C, R, wq, wc, freq, rdims, positions, slots, cq, k_cache, float(eps), T,
-                         float(amp))
+                         float(amp), freq_lo)
 
 
-def rot_heads(src, off, dst, H, Dh, freq, rdims, positions, T, slots=None, roff=0, amp=1.0):
+def split_frequencies(freq64, device):
+    """float64 rotary frequencies -> (high, low) float32 tables with high + low = the frequency to 48 bits; the rotation
+    kernels correct their fp32 angle by the low part and by what the rounded product lost"""
+    f = torch.as_tensor(freq64, dtype=torch.float64)
+    hi = f.to(torch.float32)
+    lo = (f - hi.to(torch.float64)).to(torch.float32)
+    return hi.to(device).contiguous(), lo.to(device).contiguous()
+
+
+def rot_heads(src, off, dst, H, Dh, freq, rdims, positions, T, slots=None, roff=0, amp=1.0, freq_lo=None):
     """``dst`` [T, H * Dh] (dense) = the ``H`` heads of ``Dh`` channels at column ``off`` of ``src`` with rotary positions
     on ``rdims`` channels (pairs 2i, 2i+1) of each head, from channel ``roff`` of the head on; ``amp`` multiplies cos and sin"""
-    native().rot_heads(src, off, dst, H, Dh, freq, rdims, positions, slots, T, int(roff), float(amp))
+    native().rot_heads(src, off, dst, H, Dh, freq, rdims, positions, slots, T, int(roff), float(amp), freq_lo)
 
 
 def moe_route(proj, off, corr, n_real, count, keep, top, scale, wt, idw, T, sel_idx=None, sel_w=None):

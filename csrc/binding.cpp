@@ -674,29 +674,31 @@ void post_norm_join(const Tensor& x, const OptT& rows, int64_t n_rows, const Opt
 
 void latent_prep(const Tensor& proj, int64_t off_q, int64_t q_rank, int64_t off_kv, int64_t C, int64_t R, const Tensor& wq,
                  const Tensor& wc, const Tensor& freq, int64_t rdims, const Tensor& positions, const Tensor& slots,
-                 const Tensor& cq, const Tensor& k_cache, double eps, int64_t T, double amp) {
+                 const Tensor& cq, const Tensor& k_cache, double eps, int64_t T, double amp, const OptT& freq_lo) {
   c10::cuda::CUDAGuard guard(proj.device());
   TORCH_CHECK(cq.scalar_type() == k_cache.scalar_type(), "latent_prep: operand and cache dtypes must match");
   TORCH_CHECK(k_cache.size(-1) == R + C && k_cache.is_contiguous(), "latent_prep: cache rows are [rotary | latent]");
   TORCH_CHECK(rdims == 0 || freq.numel() >= rdims / 2, "latent_prep: frequency table too short");
+  TORCH_CHECK(!(freq_lo.has_value() && freq_lo->defined()) || freq_lo->numel() >= rdims / 2, "latent_prep: low parts too short");
   check(b2b::launch_latent_prep(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off_q),
                                 static_cast<int>(q_rank), static_cast<int>(off_kv), static_cast<int>(C),
                                 static_cast<int>(R), fp(wq), fp(wc), fp(freq), static_cast<int>(rdims), ip(positions),
                                 ip(slots), cq.data_ptr(), static_cast<int>(cq.stride(0)), k_cache.data_ptr(),
                                 static_cast<float>(eps), static_cast<int>(T), is_f32(cq), static_cast<float>(amp),
-                                cur_stream()),
+                                fp_or_null(freq_lo), cur_stream()),
         "latent_prep");
 }
 
 void rot_heads(const Tensor& src, int64_t off, const Tensor& dst, int64_t H, int64_t Dh, const Tensor& freq, int64_t rdims,
-               const Tensor& positions, const OptT& slots, int64_t T, int64_t roff, double amp) {
+               const Tensor& positions, const OptT& slots, int64_t T, int64_t roff, double amp, const OptT& freq_lo) {
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(rdims == 0 || freq.numel() >= rdims / 2, "rot_heads: frequency table too short");
+  TORCH_CHECK(!(freq_lo.has_value() && freq_lo->defined()) || freq_lo->numel() >= rdims / 2, "rot_heads: low parts too short");
   TORCH_CHECK(dst.is_contiguous() && dst.size(-1) == H * Dh, "rot_heads: dense [T, H * Dh] output");
   check(b2b::launch_rot_heads(fp(src), static_cast<int>(src.stride(0)), static_cast<int>(off), const_cast<float*>(fp(dst)),
                               static_cast<int>(H), static_cast<int>(Dh), fp(freq), static_cast<int>(rdims), ip(positions),
                               (slots.has_value() && slots->defined()) ? ip(*slots) : nullptr, static_cast<int>(T),
-                              static_cast<int>(roff), static_cast<float>(amp), cur_stream()),
+                              static_cast<int>(roff), static_cast<float>(amp), fp_or_null(freq_lo), cur_stream()),
         "rot_heads");
 }
 

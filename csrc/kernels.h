@@ -126,16 +126,19 @@ int launch_scan_post(const float* o, int ld_o, const float* gate, int ld_g, int 
 // postnorm.cu: post-norm layers (grouped RMS norm behind the residual addition, scaled skip, sigmoid-gated sublayer results), latent
 // attention prep (normed query latent; cache row = [rotated shared key part | normed latent]), rotary positions on the first
 // channels of every head (-> dense query rows), softmax router (selection-only correction, group-limited top-k, identity experts),
-// act(a) * b over column blocks or per-expert weights.  ldv of launch_softmax_attention: row stride of the value view
+// act(a) * b over column blocks or per-expert weights.  freq_lo (optional): low parts of the rotary frequencies (frequency =
+// freq + freq_lo in double-float form), so that angles at far positions keep their last bits.  ldv of launch_softmax_attention: row stride of the value view
 // (0 = a cache of its own) so that values can be a slice of the key rows.
 int launch_post_norm_join(float* x, const int* rows, int n_rows, const float* y, int ld_y, const float* gate, int ld_g,
                           int off_g, const float* gbias, const float* idw, float alpha, const float* w, int groups,
                           float eps, void* h, int ld_h, int W, int f32, cudaStream_t s);
 int launch_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int C, int R, const float* wq,
                        const float* wc, const float* freq, int rdims, const int* positions, const int* slots, void* cq,
-                       int ld_cq, void* k_cache, float eps, int T, int f32, float amp, cudaStream_t s);
+                       int ld_cq, void* k_cache, float eps, int T, int f32, float amp, const float* freq_lo,
+                       cudaStream_t s);
 int launch_rot_heads(const float* src, int ld, int off, float* dst, int H, int Dh, const float* freq, int rdims,
-                     const int* positions, const int* slots, int T, int roff, float amp, cudaStream_t s);
+                     const int* positions, const int* slots, int T, int roff, float amp, const float* freq_lo,
+                     cudaStream_t s);
 int launch_moe_route(const float* proj, int ld, int off, const float* corr, int E, int n_real, int count, int keep,
                      int top, float scale, float* wt, int ld_wt, float* idw, int* sel_idx, float* sel_w, int T,
                      cudaStream_t s);

@@ -48,6 +48,19 @@ __device__ __forceinline__ float warp_max_(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+// sin and cos of position * frequency with the frequency given as a sum of two floats (flo may be 0): the fp32 product
+// pos * fhi is corrected by what its rounding lost (an exact fused multiply-add) and by pos * flo, through the addition
+// formulas with the small remainder r.  At position 1000 a plain fp32 product is off
+// by up to 3e-5 rad, which a sharp softmax over far keys shows; this form is good to the last bits of the result.
+__device__ __forceinline__ void turn_(float pos, float fhi, float flo, float* sn, float* cs) {
+  const float a = __fmul_rn(pos, fhi);
+  const float r = __fmaf_rn(pos, flo, __fmaf_rn(pos, fhi, -a));
+  float s, c, sr, cr;
+  sincosf(a, &s, &c);
+  sincosf(r, &sr, &cr);
+  *sn = __fmaf_rn(s, cr, c * sr);
+  *cs = __fmaf_rn(c, cr, -s * sr);
+}
 // ------------------------------------------------------------------------------------------- post-norm join
 // One warp per (row, group).  rows == nullptr: row = token, x is updated in place and h[t] written.  rows != nullptr:
 // row r reads token rows[r] and only writes h[r] (the logit rows in front of the model norm).
@@ -194,7 +207,8 @@ __global__ void __launch_bounds__(32 * LAT_WARPS)
     latent_prep_kernel(const float* __restrict__ proj, int ld, int off_q, int q_rank, int off_kv, int C, int R,
                        const float* __restrict__ wq, const float* __restrict__ wc, const float* __restrict__ freq,
                        int rdims, const int* __restrict__ positions, const int* __restrict__ slots, OT* __restrict__ cq,
-                       int ld_cq, CT* __restrict__ k_cache, float eps, int T, float amp) {
+                       int ld_cq, CT* __restrict__ k_cache, float eps, int T, float amp,
+                       const float* __restrict__ freq_lo) {
   pdl_begin();
   const int t = blockIdx.x * LAT_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -215,7 +229,7 @@ __global__ void __launch_bounds__(32 * LAT_WARPS)
   const float pos = static_cast<float>(positions[t]);
   for (int i = lane; i < rdims / 2; i += 32) {        // a lane turns whole pairs
     float sn, cs;
-    sincosf(pos * freq[i], &sn, &cs);
+    turn_(pos, freq[i], freq_lo != nullptr ? freq_lo[i] : 0.f, &sn, &cs);
     sn *= amp;
     cs *= amp;
     const float u = kr[2 * i], v = kr[2 * i + 1];
@@ -229,7 +243,8 @@ __global__ void __launch_bounds__(32 * LAT_WARPS)
 // channels from channel roff of every head on turned by positions[t] * freq[pair] (pairs 2i, 2i+1) and multiplied by amp.
 __global__ void rot_heads_kernel(const float* __restrict__ src, int ld, int off, float* __restrict__ dst, int H, int Dh,
                                  const float* __restrict__ freq, int rdims, const int* __restrict__ positions,
-                                 const int* __restrict__ slots, int T, int roff, float amp) {
+                                 const int* __restrict__ slots, int T, int roff, float amp,
+                                 const float* __restrict__ freq_lo) {
   pdl_begin();
   const int n = H * Dh;
   const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -241,7 +256,7 @@ __global__ void rot_heads_kernel(const float* __restrict__ src, int ld, int off,
   float v = row[c];
   if (d >= 0 && d < rdims) {
     float sn, cs;
-    sincosf(static_cast<float>(positions[t]) * freq[d >> 1], &sn, &cs);
+    turn_(static_cast<float>(positions[t]), freq[d >> 1], freq_lo != nullptr ? freq_lo[d >> 1] : 0.f, &sn, &cs);
     const float o = row[c - d + (d ^ 1)];             // the other channel of the pair (2i, 2i+1) of this head
     v = ((d & 1) ? v * cs + o * sn : v * cs - o * sn) * amp;
   }
@@ -630,26 +645,28 @@ int launch_post_norm_join(float* x, const int* rows, int n_rows, const float* y,
 
 int launch_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int C, int R, const float* wq,
                        const float* wc, const float* freq, int rdims, const int* positions, const int* slots, void* cq,
-                       int ld_cq, void* k_cache, float eps, int T, int f32, float amp, cudaStream_t s) {
+                       int ld_cq, void* k_cache, float eps, int T, int f32, float amp, const float* freq_lo,
+                       cudaStream_t s) {
   if (T <= 0) return 0;
   if (rdims < 0 || rdims > R || rdims % 2 != 0) return -2;
   const dim3 grid((T + LAT_WARPS - 1) / LAT_WARPS), block(32 * LAT_WARPS);
   if (f32)
     launch_kernel(latent_prep_kernel<float, float>, grid, block, 0, s, 1u, proj, ld, off_q, q_rank, off_kv, C, R, wq, wc,
-                  freq, rdims, positions, slots, static_cast<float*>(cq), ld_cq, static_cast<float*>(k_cache), eps, T, amp);
+                  freq, rdims, positions, slots, static_cast<float*>(cq), ld_cq, static_cast<float*>(k_cache), eps, T, amp, freq_lo);
   else
     launch_kernel(latent_prep_kernel<bf16, bf16>, grid, block, 0, s, 1u, proj, ld, off_q, q_rank, off_kv, C, R, wq, wc,
-                  freq, rdims, positions, slots, static_cast<bf16*>(cq), ld_cq, static_cast<bf16*>(k_cache), eps, T, amp);
+                  freq, rdims, positions, slots, static_cast<bf16*>(cq), ld_cq, static_cast<bf16*>(k_cache), eps, T, amp, freq_lo);
   return last_error();
 }
 
 int launch_rot_heads(const float* src, int ld, int off, float* dst, int H, int Dh, const float* freq, int rdims,
-                     const int* positions, const int* slots, int T, int roff, float amp, cudaStream_t s) {
+                     const int* positions, const int* slots, int T, int roff, float amp, const float* freq_lo,
+                     cudaStream_t s) {
   const long long n = static_cast<long long>(T) * H * Dh;
   if (n <= 0) return 0;
   if (roff < 0 || roff + rdims > Dh || rdims % 2 != 0) return -2;
   launch_kernel(rot_heads_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, 1u, src, ld, off, dst, H, Dh,
-                freq, rdims, positions, slots, T, roff, amp);
+                freq, rdims, positions, slots, T, roff, amp, freq_lo);
   return last_error();
 }
 

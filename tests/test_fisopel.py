@@ -442,6 +442,41 @@ def test_latent_prep_without_query_latent_and_amplitude(C, R, rdims, H, amp):
 
 
 @gpu
+def test_rotation_keeps_its_bits_at_far_positions():
+    """frequencies handed over as high + low floats: at positions of a thousand to a million the turned channels agree with
+    the float64 rotation to a few 1e-6, where a plain fp32 product position * frequency is off by 1e-4 to 1e-1 rad"""
+    from bee2bee_b200 import ops
+
+    dev, H, Dh, rdims, base = "cuda", 2, 24, 16, 10000.0
+    pos = torch.tensor([0, 1000, 4097, 65537, 1000003])
+    T = len(pos)
+    rot = {"dims": rdims, "base": base, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    w, amp = O.rotary_table(rot)
+    hi, lo = ops.split_frequencies(w.tolist(), dev)
+    assert float((hi.double().cpu() + lo.double().cpu() - w).abs().max()) < 1e-14
+    g = torch.Generator().manual_seed(3)
+    src = torch.randn(T, H * Dh, generator=g)
+    hv = src.double().view(T, H, Dh)
+    halves = torch.cat([hv[..., 0:rdims:2], hv[..., 1:rdims:2], hv[..., rdims:]], -1)
+    turned = O.rotate_split_halves(halves, pos, rot)
+    want = hv.clone()
+    want[..., 0:rdims:2], want[..., 1:rdims:2] = turned[..., :rdims // 2], turned[..., rdims // 2:rdims]
+    dst = torch.zeros(T, H * Dh, device=dev)
+    ops.rot_heads(src.to(dev), 0, dst, H, Dh, hi, rdims, pos.int().to(dev), T, amp=amp, freq_lo=lo)
+    assert float((dst.cpu().double() - want.reshape(T, H * Dh)).abs().max()) < 5e-6
+    cache = torch.zeros((1, 64, 1, rdims + 8), device=dev)
+    proj = torch.randn(T, rdims + 8, generator=g)
+    ops.latent_prep(proj.to(dev), 0, 0, 0, 8, rdims, hi, torch.ones(8, device=dev), hi, rdims, pos.int().to(dev),
+                    torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, 64, device=dev), cache, 1e-5, T, amp=amp,
+                    freq_lo=lo)
+    kr = proj[:, 8:].double()
+    kt = O.rotate_split_halves(torch.cat([kr[:, 0::2], kr[:, 1::2]], -1), pos, rot)
+    wk = torch.zeros(T, rdims, dtype=torch.float64)
+    wk[:, 0::2], wk[:, 1::2] = kt[:, :rdims // 2], kt[:, rdims // 2:]
+    assert float((cache.view(64, -1)[:T, :rdims].cpu().double() - wk).abs().max()) < 5e-6
+
+
+@gpu
 @pytest.mark.parametrize("E,top", [(12, 2), (5, 5), (7, 1), (64, 6), (3, 2)])
 def test_router_kernel_on_logits(E, top):
     from bee2bee_b200 import ops
